@@ -1,0 +1,149 @@
+/*
+ * quest_b200 - C ABI of the B200 (sm_100a) implementation of QuEST's W4A4 inference linear layer.
+ *
+ * Every entry point below replaces one launcher that the reference's torch C++ bindings call
+ * (gemm-quest/quest/{quantize,matmul,fused_matmul_dequantize}.cpp).  Names, argument order and
+ * argument meaning are the reference's; the differences are:
+ *   - C linkage (the reference declares them with C++ linkage inside its extension),
+ *   - every function returns an int status (QB200_OK == 0) instead of void / an ignored int,
+ *   - `do_dequantize` is an int (0/1) instead of a C++ bool.
+ *
+ * Conventions shared by all entry points
+ *   - All pointers are DEVICE pointers owned by the caller.  Nothing is allocated or freed here.
+ *   - Work is only enqueued on `stream`; no call synchronises the device.  The current device
+ *     must be the one that owns the buffers (the Python wrapper sets it).
+ *   - Matrices are dense row-major.  "packed int4" means one byte holds two two's-complement
+ *     4-bit codes: column 2j in the low nibble, column 2j+1 in the high nibble.
+ *   - bf16 means __nv_bfloat16, int32 means int32_t.
+ *   - All calls may be captured in a CUDA graph (no allocation, no synchronisation; tensor maps
+ *     are passed by value as kernel parameters).
+ */
+#ifndef QUEST_B200_H_
+#define QUEST_B200_H_
+
+#include <cuda_runtime_api.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    QB200_OK = 0,
+    QB200_ERR_INVALID_ARGUMENT = 1, /* null pointer, non-positive size, misaligned buffer */
+    QB200_ERR_UNSUPPORTED = 2,      /* shape outside what the kernels cover (see each function) */
+    QB200_ERR_CUDA = 3,             /* a CUDA runtime call or kernel launch failed */
+    QB200_ERR_DRIVER = 4,           /* cuTensorMapEncodeTiled unavailable or failed */
+    QB200_ERR_DEVICE_TIMEOUT = 5    /* a bounded in-kernel wait gave up (reported by quest_b200_device_status) */
+};
+
+/* Human-readable text for a status code. */
+const char* quest_b200_error_string(int status);
+
+/* Library version (major * 100 + minor). */
+int quest_b200_version(void);
+
+/*
+ * Reads and clears the device-side status word of the current device.  The GEMM kernel's waits on
+ * mbarriers are bounded; if one gives up, the kernel records QB200_ERR_DEVICE_TIMEOUT here, drains
+ * and returns instead of hanging.  Synchronises the device.  *status receives the recorded code.
+ */
+int quest_b200_device_status(int* status);
+
+/*
+ * scale[m] = bf16( sqrt(mean_k x[m,k]^2) * (2.513930578568423 * 2 / 15) + 1e-8 )
+ * Replaces find_scale_int4_cuda_bf16, gemm-quest/quest/quantize.cpp:5-11
+ * (kernel gemm-quest/quest/quantize_kernel.cu:38-117).
+ *   scale_ptr : bf16 [batch_size]          x_ptr : bf16 [batch_size, group_size]
+ */
+int find_scale_int4_cuda_bf16(void* scale_ptr, const void* x_ptr, int group_size, int batch_size,
+                              cudaStream_t stream);
+
+/*
+ * q = clamp(floor(x / scale), -8, 7) per row, with optional outputs (pass NULL to skip):
+ *   x_int_ptr          int8  [batch_size, group_size]      dense codes
+ *   x_int_packed_ptr   uint8 [batch_size, group_size / 2]  packed codes (group_size must be even)
+ *   x_int_row_sum_ptr  int32 [batch_size]                  sum of the codes of each row
+ * If do_dequantize != 0, x is overwritten in place by bf16((q + 0.5) * scale).
+ * Replaces quantize_int4_cuda_bf16, gemm-quest/quest/quantize.cpp:28-38
+ * (kernel gemm-quest/quest/quantize_kernel.cu:120-261).
+ */
+int quantize_int4_cuda_bf16(void* x_ptr, const void* scale_ptr, void* x_int_ptr, void* x_int_packed_ptr,
+                            void* x_int_row_sum_ptr, int group_size, int batch_size, int do_dequantize,
+                            cudaStream_t stream);
+
+/*
+ * D[m,n] = bf16( float(2*C[m,n] + a_add[m] + b_add[n]) * (0.5f * a_mul[m] * b_mul[n]) )
+ * Replaces add_mul_vv_cuda_bf16, gemm-quest/quest/quantize.cpp:73-83
+ * (kernel gemm-quest/quest/quantize_kernel.cu:264-341).
+ *   mat_d bf16 [size_a,size_b]; vec_a_add int32 [size_a]; vec_a_mul bf16 [size_a];
+ *   vec_b_add int32 [size_b]; vec_b_mul bf16 [size_b]; mat_c int32 [size_a,size_b]
+ */
+int add_mul_vv_cuda_bf16(void* mat_d, const void* vec_a_add, const void* vec_a_mul, const void* vec_b_add,
+                         const void* vec_b_mul, const void* mat_c, int size_a, int size_b, cudaStream_t stream);
+
+/*
+ * C[M,N] (int32) = A[M,K] . B[N,K]^T, both operands packed int4 (A: [M,K/2] bytes, B: [N,K/2] bytes).
+ * The accumulators are exact.  Requires K % 32 == 0 (16-byte row pitch, as the reference's CUTLASS
+ * kernel does), K < 131072, and 16-byte aligned A and B.
+ * Replaces matmul_int4_int4t_int32_cuda, gemm-quest/quest/matmul.cpp:5-13
+ * (kernel gemm-quest/quest/matmul_kernel.cu:8-63).
+ */
+int matmul_int4_int4t_int32_cuda(void* mat_c, const void* mat_a, const void* mat_b, int M, int K, int N,
+                                 cudaStream_t stream);
+
+/*
+ * D[M,N] (bf16) = add_mul_vv(vec_a_add, vec_a_mul, vec_b_add, vec_b_mul, A . B^T) in one kernel:
+ *   D[m,n] = bf16( float(2*acc + vec_a_add[m] + vec_b_add[n]) * (0.5f * vec_a_mul[m] * vec_b_mul[n]) )
+ * with exact int32 accumulators (the reference's fused epilogue rounds the accumulator to fp16
+ * first, gemm-quest/include/symmetric/epilogue/thread/linear_combination_dequant.h:133-144; this
+ * library evaluates the exact expression of add_mul_vv instead).  Same shape rules as the int32 GEMM.
+ * Replaces fused_matmul_dequantize_int4_int4t_bf16_cuda,
+ * gemm-quest/quest/fused_matmul_dequantize.cpp:5-17 (kernel .../fused_matmul_dequantize_kernel.cu:4-57).
+ *   vec_a_add int32 [M], vec_b_add int32 [N], vec_a_mul bf16 [M], vec_b_mul bf16 [N]
+ */
+int fused_matmul_dequantize_int4_int4t_bf16_cuda(void* mat_d, const void* mat_a, const void* mat_b,
+                                                 const void* vec_a_add, const void* vec_b_add,
+                                                 const void* vec_a_mul, const void* vec_b_mul, int M, int K,
+                                                 int N, cudaStream_t stream);
+
+/*
+ * As above, but the output tile columns are written into a wider row-major matrix: element (m,n)
+ * goes to mat_d[m * ld_d + n].  Used by the column-sharded multi-GPU layer, where each rank
+ * computes N_local output columns of a [M, N_total] result (ld_d = N_total, mat_d already offset
+ * to the rank's first column).  ld_d and the offset must keep 16-byte alignment of each row segment
+ * for the vector store path; otherwise a scalar store path is used.
+ * No counterpart in the reference (its inference path is single-GPU).
+ */
+int fused_matmul_dequantize_int4_int4t_bf16_strided_cuda(void* mat_d, long long ld_d, const void* mat_a,
+                                                         const void* mat_b, const void* vec_a_add,
+                                                         const void* vec_b_add, const void* vec_a_mul,
+                                                         const void* vec_b_mul, int M, int K, int N,
+                                                         cudaStream_t stream);
+
+/*
+ * Fused block-Hadamard + scale + int4 quantise + pack + row-sum of bf16 activations, one pass over
+ * x.  Per row: xh = bf16(H_block . x) blockwise along K (Sylvester order, entries +-bf16(block^-0.5)),
+ * scale = find_scale(xh), codes = quantize(xh, scale).  Replaces the three launches of the reference's
+ * layer code, gemm-quest/benchmarks/utils.py:89-100 (cuBLAS Hadamard GEMM, find_scale_int4,
+ * quantize_int4).  block in {64, 128, 256}; group_size % block == 0; group_size <= 65536.
+ *   x_int_packed_ptr uint8 [batch_size, group_size/2]; scale_ptr bf16 [batch_size];
+ *   x_int_row_sum_ptr int32 [batch_size] (may be NULL); x_ptr bf16 [batch_size, group_size] (read only)
+ */
+int hadamard_quantize_int4_cuda_bf16(void* x_int_packed_ptr, void* scale_ptr, void* x_int_row_sum_ptr,
+                                     const void* x_ptr, int group_size, int batch_size, int block,
+                                     cudaStream_t stream);
+
+/*
+ * out = bf16(H_block . x) blockwise along the last dimension (out may alias x).
+ * weight_side == 0: entries +-bf16(block^-0.5), the activation-side matrix of
+ * gemm-quest/benchmarks/utils.py:17,89-90.  weight_side != 0: entries +-fp32(block^-0.5), the
+ * weight-side call hadamard_transform(..., scale=2**-3.5) of gemm-quest/benchmarks/utils.py:38-39.
+ */
+int hadamard_transform_cuda_bf16(void* out_ptr, const void* x_ptr, int group_size, int batch_size, int block,
+                                 int weight_side, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* QUEST_B200_H_ */

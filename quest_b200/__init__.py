@@ -1,0 +1,199 @@
+"""quest_b200 - drop-in replacement of the reference's ``quest`` op package on B200 (sm_100a).
+
+The dense ops keep the signatures, dtype/contiguity asserts, output allocation and return conventions
+of gemm-quest/quest/__init__.py; each forwards raw device pointers to one ``extern "C"`` entry point
+of ``libquest_b200.so`` on the current CUDA stream of the tensors' device.  Two ops are new:
+``hadamard_quantize_int4`` (the fused kernel that replaces the Hadamard GEMM + find_scale + quantize
+launches of the reference's ``linear_forward``) and ``hadamard_transform``.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._lib import device_status  # noqa: F401
+
+
+def _call(name: str, device: torch.device, *args) -> None:
+    fn = getattr(_lib.load(), name)
+    if torch.cuda.current_device() != device.index:
+        with torch.cuda.device(device):
+            _lib.check(fn(*args), name)
+    else:
+        _lib.check(fn(*args), name)
+
+
+def fused_matmul_dequantize_int4_int4t_bf16(
+        mat_a: torch.Tensor,
+        mat_b: torch.Tensor,
+        vec_a_add: torch.Tensor,
+        vec_b_add: torch.Tensor,
+        vec_a_mul: torch.Tensor,
+        vec_b_mul: torch.Tensor,
+        out: torch.Tensor = None,
+) -> torch.Tensor:
+    """out[M,N] bf16 = add_mul_vv(vec_a_add, vec_a_mul, vec_b_add, vec_b_mul, mat_a @ mat_b^T) in one kernel.
+    Mirrors gemm-quest/quest/__init__.py:6-20."""
+    if out is None:
+        out = torch.empty(mat_a.size(0), mat_b.size(0), dtype=torch.bfloat16, device=mat_a.device)
+    assert mat_a.dtype == torch.uint8 and mat_b.dtype == torch.uint8 and vec_a_add.dtype == torch.int32 and vec_b_add.dtype == torch.int32 and vec_a_mul.dtype == torch.bfloat16 and vec_b_mul.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    assert mat_a.is_contiguous() and mat_b.is_contiguous() and vec_a_add.is_contiguous() and vec_b_add.is_contiguous() and vec_a_mul.is_contiguous() and vec_b_mul.is_contiguous() and out.is_contiguous()
+    dev = _lib.require_cuda(mat_a, mat_b, vec_a_add, vec_b_add, vec_a_mul, vec_b_mul, out)
+    _call("fused_matmul_dequantize_int4_int4t_bf16_cuda", dev, _lib.ptr(out), _lib.ptr(mat_a), _lib.ptr(mat_b),
+          _lib.ptr(vec_a_add), _lib.ptr(vec_b_add), _lib.ptr(vec_a_mul), _lib.ptr(vec_b_mul),
+          mat_a.size(0), mat_b.size(1) * 2, mat_b.size(0), _lib.stream_of(out))
+    return out
+
+
+def fused_matmul_dequantize_int4_int4t_bf16_into(
+        mat_a: torch.Tensor,
+        mat_b: torch.Tensor,
+        vec_a_add: torch.Tensor,
+        vec_b_add: torch.Tensor,
+        vec_a_mul: torch.Tensor,
+        vec_b_mul: torch.Tensor,
+        out_cols: torch.Tensor,
+) -> torch.Tensor:
+    """Same computation, written into a column slice ``out_cols = full[:, n0:n0+N]`` of a wider
+    row-major bf16 matrix (row stride = out_cols.stride(0)).  Used by the column-sharded layer."""
+    assert out_cols.dtype == torch.bfloat16 and out_cols.dim() == 2 and out_cols.stride(1) == 1
+    assert out_cols.size(0) == mat_a.size(0) and out_cols.size(1) == mat_b.size(0)
+    assert mat_a.dtype == torch.uint8 and mat_b.dtype == torch.uint8 and vec_a_add.dtype == torch.int32 and vec_b_add.dtype == torch.int32 and vec_a_mul.dtype == torch.bfloat16 and vec_b_mul.dtype == torch.bfloat16
+    assert mat_a.is_contiguous() and mat_b.is_contiguous() and vec_a_add.is_contiguous() and vec_b_add.is_contiguous() and vec_a_mul.is_contiguous() and vec_b_mul.is_contiguous()
+    dev = _lib.require_cuda(mat_a, mat_b, vec_a_add, vec_b_add, vec_a_mul, vec_b_mul, out_cols)
+    _call("fused_matmul_dequantize_int4_int4t_bf16_strided_cuda", dev, _lib.ptr(out_cols), out_cols.stride(0),
+          _lib.ptr(mat_a), _lib.ptr(mat_b), _lib.ptr(vec_a_add), _lib.ptr(vec_b_add), _lib.ptr(vec_a_mul),
+          _lib.ptr(vec_b_mul), mat_a.size(0), mat_b.size(1) * 2, mat_b.size(0), _lib.stream_of(out_cols))
+    return out_cols
+
+
+def matmul_int4_int4t_int32(
+        mat_a: torch.Tensor,
+        mat_b: torch.Tensor,
+        out: torch.Tensor = None,
+) -> torch.Tensor:
+    """out[M,N] int32 = mat_a[M,K/2] @ mat_b[N,K/2]^T on packed int4 codes, exact.
+    Mirrors gemm-quest/quest/__init__.py:23-33."""
+    if out is None:
+        out = torch.empty(mat_a.size(0), mat_b.size(0), dtype=torch.int32, device=mat_a.device)
+    assert mat_a.dtype == torch.uint8 and mat_b.dtype == torch.uint8 and out.dtype == torch.int32
+    assert mat_a.is_contiguous() and mat_b.is_contiguous() and out.is_contiguous()
+    dev = _lib.require_cuda(mat_a, mat_b, out)
+    _call("matmul_int4_int4t_int32_cuda", dev, _lib.ptr(out), _lib.ptr(mat_a), _lib.ptr(mat_b),
+          mat_a.size(0), mat_b.size(1) * 2, mat_b.size(0), _lib.stream_of(out))
+    return out
+
+
+def matmul_int4sp_int4t_int32(*args, **kwargs):
+    """4:8-sparse GEMM of the reference (gemm-quest/quest/__init__.py:36-47): not part of the dense path."""
+    raise NotImplementedError("quest_b200 implements the dense W4A4 path only")
+
+
+def reorder_meta48_int4(*args, **kwargs):
+    raise NotImplementedError("quest_b200 implements the dense W4A4 path only")
+
+
+def uncompress_meta48_int4(*args, **kwargs):
+    raise NotImplementedError("quest_b200 implements the dense W4A4 path only")
+
+
+def generate_random_meta48_int4(*args, **kwargs):
+    raise NotImplementedError("quest_b200 implements the dense W4A4 path only")
+
+
+def find_scale_int4(
+        x: torch.Tensor,
+        scale: torch.Tensor = None,
+) -> torch.Tensor:
+    """scale[M,1] = sqrt(mean(x^2)) * (2.5139 * 2 / 15) + 1e-8 in x's dtype.
+    Mirrors gemm-quest/quest/__init__.py:87-96."""
+    if scale is None:
+        scale = torch.empty(x.size(0), 1, dtype=x.dtype, device=x.device)
+    assert x.dtype == torch.bfloat16 and scale.dtype == torch.bfloat16
+    assert x.is_contiguous() and scale.is_contiguous()
+    dev = _lib.require_cuda(x, scale)
+    _call("find_scale_int4_cuda_bf16", dev, _lib.ptr(scale), _lib.ptr(x), x.size(1), x.size(0), _lib.stream_of(x))
+    return scale
+
+
+def quantize_int4(
+        x: torch.Tensor,
+        scale: torch.Tensor,
+        x_int: torch.Tensor = None,
+        x_int_packed: torch.Tensor = None,
+        x_int_row_sum: torch.Tensor = None,
+        do_dequantize: bool = False,
+) -> tuple[torch.Tensor, torch.Tensor | None, torch.Tensor | None, torch.Tensor | None]:
+    """Floor-quantise x by its per-row scale into any of: dense int8 codes, packed codes, int32 row
+    sums; optionally overwrite x with the dequantised values.  Returns the caller's own objects
+    (None where not supplied).  Mirrors gemm-quest/quest/__init__.py:99-114."""
+    assert x.dtype == torch.bfloat16 and scale.dtype == torch.bfloat16 and (x_int is None or x_int.dtype == torch.int8) and (x_int_packed is None or x_int_packed.dtype == torch.uint8) and (x_int_row_sum is None or x_int_row_sum.dtype == torch.int32)
+    assert x.is_contiguous() and scale.is_contiguous() and (x_int is None or x_int.is_contiguous()) and (x_int_packed is None or x_int_packed.is_contiguous()) and (x_int_row_sum is None or x_int_row_sum.is_contiguous())
+    dev = _lib.require_cuda(x, scale, x_int, x_int_packed, x_int_row_sum)
+    _call("quantize_int4_cuda_bf16", dev, _lib.ptr(x), _lib.ptr(scale), _lib.ptr(x_int), _lib.ptr(x_int_packed),
+          _lib.ptr(x_int_row_sum), x.size(1), x.size(0), int(bool(do_dequantize)), _lib.stream_of(x))
+    return x, x_int, x_int_packed, x_int_row_sum
+
+
+def add_mul_vv(
+        vec_a_add: torch.Tensor,
+        vec_a_mul: torch.Tensor,
+        vec_b_add: torch.Tensor,
+        vec_b_mul: torch.Tensor,
+        mat_c: torch.Tensor,
+        mat_d: torch.Tensor = None,
+) -> torch.Tensor:
+    """mat_d = float(2 * mat_c + vec_a_add + vec_b_add^T) * (0.5 * vec_a_mul * vec_b_mul^T) -> bf16.
+    Mirrors gemm-quest/quest/__init__.py:117-130."""
+    if mat_d is None:
+        mat_d = torch.empty(mat_c.shape, dtype=vec_a_mul.dtype, device=mat_c.device)
+    assert vec_a_add.dtype == torch.int32 and vec_a_mul.dtype == torch.bfloat16 and vec_b_add.dtype == torch.int32 and vec_b_mul.dtype == torch.bfloat16 and mat_c.dtype == torch.int32 and mat_d.dtype == torch.bfloat16
+    assert vec_a_add.is_contiguous() and vec_a_mul.is_contiguous() and vec_b_add.is_contiguous() and vec_b_mul.is_contiguous() and mat_c.is_contiguous() and mat_d.is_contiguous()
+    dev = _lib.require_cuda(vec_a_add, vec_a_mul, vec_b_add, vec_b_mul, mat_c, mat_d)
+    _call("add_mul_vv_cuda_bf16", dev, _lib.ptr(mat_d), _lib.ptr(vec_a_add), _lib.ptr(vec_a_mul), _lib.ptr(vec_b_add),
+          _lib.ptr(vec_b_mul), _lib.ptr(mat_c), mat_c.size(0), mat_c.size(1), _lib.stream_of(mat_c))
+    return mat_d
+
+
+def hadamard_quantize_int4(
+        x: torch.Tensor,
+        block: int = 128,
+        x_int_packed: torch.Tensor = None,
+        scale: torch.Tensor = None,
+        x_int_row_sum: torch.Tensor = None,
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Fused block-Hadamard + find_scale_int4 + quantize_int4 (packed codes + row sums) in one pass over x.
+    x is not modified.  Equivalent to gemm-quest/benchmarks/utils.py:89-100 with use_hadamard=True.
+    Returns (x_int_packed [M,K/2] u8, scale [M,1] bf16, x_int_row_sum [M,1] i32)."""
+    assert x.dim() == 2
+    m, k = x.shape
+    if x_int_packed is None:
+        x_int_packed = torch.empty(m, k // 2, dtype=torch.uint8, device=x.device)
+    if scale is None:
+        scale = torch.empty(m, 1, dtype=x.dtype, device=x.device)
+    if x_int_row_sum is None:
+        x_int_row_sum = torch.empty(m, 1, dtype=torch.int32, device=x.device)
+    assert x.dtype == torch.bfloat16 and scale.dtype == torch.bfloat16 and x_int_packed.dtype == torch.uint8 and x_int_row_sum.dtype == torch.int32
+    assert x.is_contiguous() and scale.is_contiguous() and x_int_packed.is_contiguous() and x_int_row_sum.is_contiguous()
+    dev = _lib.require_cuda(x, scale, x_int_packed, x_int_row_sum)
+    _call("hadamard_quantize_int4_cuda_bf16", dev, _lib.ptr(x_int_packed), _lib.ptr(scale), _lib.ptr(x_int_row_sum),
+          _lib.ptr(x), k, m, int(block), _lib.stream_of(x))
+    return x_int_packed, scale, x_int_row_sum
+
+
+def hadamard_transform(x: torch.Tensor, block: int = 128, weight_side: bool = False, out: torch.Tensor = None) -> torch.Tensor:
+    """bf16(H_block @ x) blockwise along the last dim.  ``weight_side`` selects the exact fp32
+    normalisation of gemm-quest/benchmarks/utils.py:39 instead of the bf16 one of utils.py:17."""
+    assert x.dtype == torch.bfloat16 and x.is_contiguous()
+    if out is None:
+        out = torch.empty_like(x)
+    assert out.dtype == torch.bfloat16 and out.is_contiguous() and out.shape == x.shape
+    k = x.size(-1)
+    m = x.numel() // k if k else 0
+    dev = _lib.require_cuda(x, out)
+    _call("hadamard_transform_cuda_bf16", dev, _lib.ptr(out), _lib.ptr(x), k, m, int(block), int(bool(weight_side)),
+          _lib.stream_of(x))
+    return out
+
+
+from .layer import Linear4bit, linear_forward, preprocess_weight, unpack_int4  # noqa: E402,F401

@@ -1,0 +1,52 @@
+// Shared helpers for the sm_100a kernels of the W4A4 linear path.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/quest_b200.h"
+
+namespace qb {
+
+// ---------------------------------------------------------------------------------------------
+// Host-side helpers
+// ---------------------------------------------------------------------------------------------
+inline int cuda_status(cudaError_t e) { return e == cudaSuccess ? QB200_OK : QB200_ERR_CUDA; }
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Launch errors are sticky per thread; peek (do not clear another library's error) after each launch.
+inline int launch_status() { return cuda_status(cudaPeekAtLastError()); }
+
+// ---------------------------------------------------------------------------------------------
+// Device-side helpers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float bf16lo_to_f32(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16hi_to_f32(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+
+// Two fp32 -> packed bf16x2 (round to nearest even); `lo` lands in bits [0,16).
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+__device__ __forceinline__ float bf16_to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+// Streaming 16-byte global load that does not allocate in L1 (data is read exactly once).
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+    uint4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+    return r;
+}
+
+// The Gaussian-MSE-optimal 4-bit clip constant and the derived step factor (2*c/15), and the eps,
+// exactly as the reference evaluates them in fp32 (gemm-quest/quest/quantize_kernel.cu:81-86).
+__device__ __forceinline__ float quest_scale_from_mean_square(float mean_sq) {
+    const float factor = 2.513930578568423f * 2.f / 15.f;
+    return sqrtf(mean_sq) * factor + 1e-8f;
+}
+
+}  // namespace qb

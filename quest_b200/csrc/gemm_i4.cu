@@ -1,0 +1,603 @@
+// Dense int4 x int4 -> int32 GEMM for sm_100a (B200), with an optional fused dequantising epilogue.
+//
+//   C[M,N] = A[M,K] . B[N,K]^T      A, B packed int4 (two codes per byte, K contiguous)
+//
+// sm_100 tensor cores have no int4 MMA, so the kernel unpacks to int8 on the fly:
+//
+//   TMA (cp.async.bulk.tensor.2d)  : packed tiles  global -> shared      (producer warp)
+//   unpack warps                   : packed shared -> int8 shared tile in the canonical K-major
+//                                    128-byte-swizzled UMMA layout
+//   tcgen05.mma kind::i8           : int8 x int8 -> int32 accumulators in tensor memory (one thread)
+//   epilogue warps                 : tcgen05.ld accumulators -> registers -> int32 or bf16 -> global
+//
+// The unpack uses the "times sixteen" form: for a 32-bit word w holding eight codes,
+//   (w << 4) & 0xF0F0F0F0  holds 16 * (codes in the low nibbles)   as four int8
+//    w       & 0xF0F0F0F0  holds 16 * (codes in the high nibbles)  as four int8
+// which needs no per-nibble sign extension.  Both operands are scaled by 16, so every product and
+// hence the accumulator is scaled by exactly 256 and the epilogue shifts it back (exact: the sum is
+// a multiple of 256; |acc| * 256 <= 2^14 * K < 2^31 for K < 2^17).  The unpack also permutes K
+// inside a 32-element group (even columns first, then odd); A and B are permuted identically, so
+// each dot product is unchanged and the accumulators are bit-exact.
+//
+// The kernel is persistent (one CTA per SM, static round-robin over output tiles), uses two
+// accumulator buffers in tensor memory so that the epilogue of tile i overlaps the main loop of
+// tile i+1, and bounds every mbarrier wait: on a timeout it records an error code in a device
+// status word, drains its copies, frees tensor memory and returns.
+//
+// Replaces gemm-quest/quest/matmul_kernel.cu:8-63 and gemm-quest/quest/fused_matmul_dequantize_kernel.cu
+// with gemm-quest/include/symmetric/** (CUTLASS 2.x Sm80 mma.sync kernels).
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace qb {
+
+__device__ int g_device_status = 0;
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait: gives up after about a second of polling, records the failure and tells the caller.
+constexpr long long kWaitLimitCycles = 2000000000LL;
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, int where) {
+    const long long t0 = clock64();
+    while (true) {
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (clock64() - t0 > kWaitLimitCycles) {
+            atomicCAS(&g_device_status, 0, (where << 8) | QB200_ERR_DEVICE_TIMEOUT);
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int where) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, where);
+}
+
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem] . B[smem]^T, int8 operands, int32 accumulate.
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 32 lanes x 32 columns of 32-bit accumulators: thread t of the warp receives lane (base + t), columns c..c+31.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 r;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"(addr));
+    return r;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------
+// Tile configuration
+// ---------------------------------------------------------------------------------------------
+constexpr int BM = 128;       // rows of A per tile = UMMA M
+constexpr int BK = 128;       // K elements per pipeline stage: 64 packed bytes, 128 int8 bytes (one swizzle row)
+constexpr int PK_ROW = BK / 2;  // packed bytes per row per stage
+constexpr int U8_ROW = BK;      // unpacked bytes per row per stage
+
+constexpr int kNumUnpackWarps = 8;
+constexpr int kNumEpilogueWarps = 4;
+constexpr int kFirstEpilogueWarp = 2;
+constexpr int kFirstUnpackWarp = kFirstEpilogueWarp + kNumEpilogueWarps;
+constexpr int kNumWarps = kFirstUnpackWarp + kNumUnpackWarps;
+constexpr int kNumThreads = kNumWarps * 32;
+
+template <int BN>
+struct Cfg {
+    static constexpr int ROWS = BM + BN;                 // A rows then B rows, contiguous in shared memory
+    static constexpr int P_STAGES = 4;                   // packed ring  (TMA -> unpack)
+    static constexpr int U_STAGES = (BN == 256) ? 2 : 3; // int8 ring    (unpack -> MMA)
+    static constexpr int P_BYTES = ROWS * PK_ROW;
+    static constexpr int U_BYTES = ROWS * U8_ROW;
+    static constexpr int TMEM_COLS = 2 * BN;             // two accumulator buffers (power of two >= 32)
+    static constexpr int NUM_BARS = 2 * P_STAGES + 2 * U_STAGES + 4 + 1;
+    static constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + U_STAGES * U_BYTES + P_STAGES * P_BYTES + NUM_BARS * 8 + 16;
+    // instruction descriptor: D=s32, A=B=s8, both K-major, N and M of the MMA
+    static constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+};
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows 128 bytes apart, 8-row
+// groups 1024 bytes apart; descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+
+struct EpilogueParams {
+    void* out;              // int32 [M, ld] or bf16 [M, ld]
+    long long ld;           // leading dimension of out, in elements
+    const int32_t* a_add;   // [M]   (fused only)
+    const int32_t* b_add;   // [N]
+    const __nv_bfloat16* a_mul;  // [M]
+    const __nv_bfloat16* b_mul;  // [N]
+    int vec_ok;             // 16-byte stores are aligned for every (row, 8-column group)
+};
+
+// ---------------------------------------------------------------------------------------------
+// The kernel
+// ---------------------------------------------------------------------------------------------
+template <int BN, bool FUSED>
+__global__ void __launch_bounds__(kNumThreads, 1)
+gemm_i4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const EpilogueParams ep, const int M, const int N, const int K) {
+    using C = Cfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t u_base = smem_base;                                   // int8 ring, 1024-byte aligned stages
+    const uint32_t p_base = u_base + C::U_STAGES * C::U_BYTES;           // packed ring
+    const uint32_t bar_base = p_base + C::P_STAGES * C::P_BYTES;         // mbarriers (8-byte aligned)
+    const uint32_t full_p = bar_base;
+    const uint32_t empty_p = full_p + 8 * C::P_STAGES;
+    const uint32_t full_u = empty_p + 8 * C::P_STAGES;
+    const uint32_t empty_u = full_u + 8 * C::U_STAGES;
+    const uint32_t tmem_full = empty_u + 8 * C::U_STAGES;
+    const uint32_t tmem_empty = tmem_full + 16;
+    const uint32_t mma_done = tmem_empty + 16;
+    const uint32_t tmem_slot = mma_done + 8;
+    volatile uint32_t* tmem_slot_ptr =
+        reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    const int tiles_m = (M + BM - 1) / BM;
+    const int tiles_n = (N + BN - 1) / BN;
+    const int num_tiles = tiles_m * tiles_n;
+    const int num_kb = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < C::P_STAGES; ++i) {
+            mbar_init(full_p + 8 * i, 1);
+            mbar_init(empty_p + 8 * i, kNumUnpackWarps);
+        }
+        for (int i = 0; i < C::U_STAGES; ++i) {
+            mbar_init(full_u + 8 * i, kNumUnpackWarps);
+            mbar_init(empty_u + 8 * i, 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(tmem_full + 8 * i, 1);
+            mbar_init(tmem_empty + 8 * i, kNumEpilogueWarps);
+        }
+        mbar_init(mma_done, 1);
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, C::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_acc = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            tma_prefetch_desc(&tmap_a);
+            tma_prefetch_desc(&tmap_b);
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % tiles_m) * BM;
+                const int n0 = (tile / tiles_m) * BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const uint32_t s = it % C::P_STAGES, ph = (it / C::P_STAGES) & 1u;
+                    if (!(ok = mbar_wait(empty_p + 8 * s, ph ^ 1u, 1))) break;
+                    mbar_arrive_expect_tx(full_p + 8 * s, C::P_BYTES);
+                    const uint32_t dst = p_base + s * C::P_BYTES;
+                    tma_load_2d(dst, &tmap_a, kb * PK_ROW, m0, full_p + 8 * s);
+                    tma_load_2d(dst + BM * PK_ROW, &tmap_b, kb * PK_ROW, n0, full_p + 8 * s);
+                }
+            }
+            // Do not leave while a copy of ours may still land in this CTA's shared memory.
+            const uint32_t pending = it < (uint32_t)C::P_STAGES ? it : (uint32_t)C::P_STAGES;
+            for (uint32_t j = 0; j < pending; ++j) {
+                const uint32_t i2 = it - 1 - j;
+                mbar_wait(full_p + 8 * (i2 % C::P_STAGES), (i2 / C::P_STAGES) & 1u, 2);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            uint32_t it = 0, local_tile = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+                const uint32_t acc = local_tile & 1u, acc_ph = (local_tile >> 1) & 1u;
+                if (!(ok = mbar_wait(tmem_empty + 8 * acc, acc_ph ^ 1u, 3))) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_acc + acc * BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const uint32_t s = it % C::U_STAGES, ph = (it / C::U_STAGES) & 1u;
+                    if (!(ok = mbar_wait(full_u + 8 * s, ph, 4))) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = u_base + s * C::U_BYTES;
+                    const uint32_t b_addr = a_addr + BM * U8_ROW;
+#pragma unroll
+                    for (int j = 0; j < BK / 32; ++j) {
+                        umma_i8(d_tmem, make_smem_desc(a_addr + 32 * j), make_smem_desc(b_addr + 32 * j), C::IDESC,
+                                (kb | j) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(empty_u + 8 * s);  // frees the int8 stage once these MMAs have read it
+                }
+                if (ok) umma_commit(tmem_full + 8 * acc);
+            }
+            // Everything issued so far must have completed before tensor memory is released.
+            umma_commit(mma_done);
+            mbar_wait(mma_done, 0, 5);
+        }
+    } else if (warp < kFirstUnpackWarp) {
+        // ------------------------------ epilogue ------------------------------
+        const int quad = warp & 3;  // tensor-memory lane quadrant this warp may read
+        uint32_t local_tile = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+            const int m0 = (tile % tiles_m) * BM;
+            const int n0 = (tile / tiles_m) * BN;
+            const uint32_t acc = local_tile & 1u, acc_ph = (local_tile >> 1) & 1u;
+            ok = mbar_wait(tmem_full + 8 * acc, acc_ph, 6);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const int row = m0 + quad * 32 + lane;
+            const bool row_ok = row < M;
+            int a_add = 0;
+            float half_a_mul = 0.f;
+            if (FUSED && row_ok) {
+                a_add = ep.a_add[row];
+                half_a_mul = 0.5f * bf16_to_f32(ep.a_mul[row]);
+            }
+            const uint32_t t_row = tmem_acc + ((uint32_t)(quad * 32) << 16) + acc * BN;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                if (n0 + c0 >= N) break;  // warp-uniform
+                uint32_t r[32];
+                tmem_ld32(t_row + c0, r);
+                tmem_ld_wait();
+                if (!row_ok) continue;
+                const int col0 = n0 + c0;
+                if (FUSED) {
+                    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(ep.out) + (size_t)row * ep.ld + col0;
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        const int col = col0 + 8 * g;
+                        if (ep.vec_ok && col + 8 <= N) {
+                            const int4 b0 = __ldg(reinterpret_cast<const int4*>(ep.b_add + col));
+                            const int4 b1 = __ldg(reinterpret_cast<const int4*>(ep.b_add + col + 4));
+                            const uint4 bm = __ldg(reinterpret_cast<const uint4*>(ep.b_mul + col));
+                            const int ba[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+                            const uint32_t bmw[4] = {bm.x, bm.y, bm.z, bm.w};
+                            uint32_t o[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int acc0 = (int)r[8 * g + 2 * i] >> 8, acc1 = (int)r[8 * g + 2 * i + 1] >> 8;
+                                const float v0 = (float)(acc0 * 2 + a_add + ba[2 * i]) * (half_a_mul * bf16lo_to_f32(bmw[i]));
+                                const float v1 = (float)(acc1 * 2 + a_add + ba[2 * i + 1]) * (half_a_mul * bf16hi_to_f32(bmw[i]));
+                                o[i] = pack_bf16x2(v0, v1);
+                            }
+                            *reinterpret_cast<uint4*>(out + 8 * g) = make_uint4(o[0], o[1], o[2], o[3]);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                if (col + i < N) {
+                                    const int acc0 = (int)r[8 * g + i] >> 8;
+                                    const float v0 = (float)(acc0 * 2 + a_add + ep.b_add[col + i]) *
+                                                     (half_a_mul * bf16_to_f32(ep.b_mul[col + i]));
+                                    out[8 * g + i] = __float2bfloat16_rn(v0);
+                                }
+                            }
+                        }
+                    }
+                } else {
+                    int32_t* out = static_cast<int32_t*>(ep.out) + (size_t)row * ep.ld + col0;
+#pragma unroll
+                    for (int g = 0; g < 8; ++g) {
+                        const int col = col0 + 4 * g;
+                        if (ep.vec_ok && col + 4 <= N) {
+                            *reinterpret_cast<int4*>(out + 4 * g) =
+                                make_int4((int)r[4 * g] >> 8, (int)r[4 * g + 1] >> 8, (int)r[4 * g + 2] >> 8, (int)r[4 * g + 3] >> 8);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                if (col + i < N) out[4 * g + i] = (int)r[4 * g + i] >> 8;
+                        }
+                    }
+                }
+            }
+            // This warp has finished reading the accumulator buffer.
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tmem_empty + 8 * acc);
+        }
+    } else {
+        // ------------------------------ unpack warps ------------------------------
+        const int t = threadIdx.x - kFirstUnpackWarp * 32;  // 0 .. 255
+        uint32_t it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const uint32_t ps = it % C::P_STAGES, pph = (it / C::P_STAGES) & 1u;
+                const uint32_t us = it % C::U_STAGES, uph = (it / C::U_STAGES) & 1u;
+                ok = mbar_wait(full_p + 8 * ps, pph, 7) && mbar_wait(empty_u + 8 * us, uph ^ 1u, 8);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                const uint32_t src = p_base + ps * C::P_BYTES;
+                const uint32_t dst = u_base + us * C::U_BYTES;
+                constexpr int ITEMS = C::ROWS * 4 / (kNumUnpackWarps * 32);
+                uint4 pk[ITEMS];
+#pragma unroll
+                for (int i = 0; i < ITEMS; ++i) {
+                    const int item = t + i * kNumUnpackWarps * 32;
+                    pk[i] = lds128(src + (item >> 2) * PK_ROW + (item & 3) * 16);
+                }
+#pragma unroll
+                for (int i = 0; i < ITEMS; ++i) {
+                    const int item = t + i * kNumUnpackWarps * 32;
+                    const int r = item >> 2, c = item & 3;
+                    uint4 lo, hi;
+                    lo.x = (pk[i].x << 4) & 0xF0F0F0F0u; hi.x = pk[i].x & 0xF0F0F0F0u;
+                    lo.y = (pk[i].y << 4) & 0xF0F0F0F0u; hi.y = pk[i].y & 0xF0F0F0F0u;
+                    lo.z = (pk[i].z << 4) & 0xF0F0F0F0u; hi.z = pk[i].z & 0xF0F0F0F0u;
+                    lo.w = (pk[i].w << 4) & 0xF0F0F0F0u; hi.w = pk[i].w & 0xF0F0F0F0u;
+                    // 16-byte chunk index is XORed with (row & 7): the 128-byte swizzle of the UMMA layout.
+                    const uint32_t rowaddr = dst + r * U8_ROW;
+                    sts128(rowaddr + (((2 * c) ^ (r & 7)) << 4), lo);
+                    sts128(rowaddr + (((2 * c + 1) ^ (r & 7)) << 4), hi);
+                }
+                fence_proxy_async_smem();  // make the generic-proxy stores visible to the tensor core
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(full_u + 8 * us);
+                    mbar_arrive(empty_p + 8 * ps);
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_acc, C::TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// Packed operand [rows, K/2] bytes, row-major; box = 64 bytes x box_rows, no swizzle, zero fill outside.
+static int make_packed_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (fn == nullptr) return QB200_ERR_DRIVER;
+    const cuuint64_t dims[2] = {(cuuint64_t)(K / 2), (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)(K / 2)};
+    const cuuint32_t box[2] = {(cuuint32_t)PK_ROW, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? QB200_OK : QB200_ERR_DRIVER;
+}
+
+static int sm_count_of_current_device(int* dev_out) {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (dev_out) *dev_out = dev;
+    if (dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+template <int BN, bool FUSED>
+static int launch_gemm(const EpilogueParams& ep, const void* a, const void* b, int M, int K, int N, int sms, int dev,
+                       cudaStream_t stream) {
+    using C = Cfg<BN>;
+    static bool attr_set[64] = {false};
+    auto kernel = gemm_i4_kernel<BN, FUSED>;
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
+            return QB200_ERR_CUDA;
+        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
+    CUtensorMap ma, mb;
+    int st = make_packed_map(&ma, a, M, K, BM);
+    if (st != QB200_OK) return st;
+    st = make_packed_map(&mb, b, N, K, BN);
+    if (st != QB200_OK) return st;
+    const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const int grid = tiles < sms ? tiles : sms;
+    kernel<<<grid, kNumThreads, C::SMEM_BYTES, stream>>>(ma, mb, ep, M, N, K);
+    return launch_status();
+}
+
+static int pick_bn(int M, int N, int sms) {
+    // Prefer the 128x256 tile (more reuse per byte of shared-memory traffic) unless the narrower tile
+    // fills the SMs clearly better.
+    auto eff = [&](int bn) {
+        const long long tiles = (long long)((M + BM - 1) / BM) * ((N + bn - 1) / bn);
+        const long long waves = (tiles + sms - 1) / sms;
+        return (double)tiles * bn / (double)(waves * sms * 256);
+    };
+    if (N <= 128) return 128;
+    return eff(128) > 1.15 * eff(256) ? 128 : 256;
+}
+
+static int run_gemm(bool fused, const EpilogueParams& ep_in, const void* a, const void* b, int M, int K, int N,
+                    cudaStream_t stream) {
+    if (M < 0 || N < 0 || K < 0) return QB200_ERR_INVALID_ARGUMENT;
+    if (M == 0 || N == 0) return QB200_OK;
+    if (ep_in.out == nullptr || a == nullptr || b == nullptr) return QB200_ERR_INVALID_ARGUMENT;
+    if (K == 0 || K % 32 != 0 || K >= (1 << 17)) return QB200_ERR_UNSUPPORTED;
+    if (!aligned16(a) || !aligned16(b)) return QB200_ERR_INVALID_ARGUMENT;
+    EpilogueParams ep = ep_in;
+    const int elem = fused ? 2 : 4;
+    const int vec_elems = 16 / elem;
+    ep.vec_ok = aligned16(ep.out) && (ep.ld % vec_elems == 0);
+    if (fused) ep.vec_ok = ep.vec_ok && aligned16(ep.b_add) && aligned16(ep.b_mul);
+    int dev = 0;
+    const int sms = sm_count_of_current_device(&dev);
+    if (sms <= 0) return QB200_ERR_CUDA;
+    const int bn = pick_bn(M, N, sms);
+    if (fused) return bn == 256 ? launch_gemm<256, true>(ep, a, b, M, K, N, sms, dev, stream)
+                                : launch_gemm<128, true>(ep, a, b, M, K, N, sms, dev, stream);
+    return bn == 256 ? launch_gemm<256, false>(ep, a, b, M, K, N, sms, dev, stream)
+                     : launch_gemm<128, false>(ep, a, b, M, K, N, sms, dev, stream);
+}
+
+}  // namespace qb
+
+using namespace qb;
+
+extern "C" int matmul_int4_int4t_int32_cuda(void* mat_c, const void* mat_a, const void* mat_b, int M, int K, int N,
+                                            cudaStream_t stream) {
+    EpilogueParams ep{};
+    ep.out = mat_c;
+    ep.ld = N;
+    return run_gemm(false, ep, mat_a, mat_b, M, K, N, stream);
+}
+
+extern "C" int fused_matmul_dequantize_int4_int4t_bf16_strided_cuda(void* mat_d, long long ld_d, const void* mat_a,
+                                                                    const void* mat_b, const void* vec_a_add,
+                                                                    const void* vec_b_add, const void* vec_a_mul,
+                                                                    const void* vec_b_mul, int M, int K, int N,
+                                                                    cudaStream_t stream) {
+    if (M > 0 && N > 0 && (!vec_a_add || !vec_b_add || !vec_a_mul || !vec_b_mul)) return QB200_ERR_INVALID_ARGUMENT;
+    if (ld_d < N) return QB200_ERR_INVALID_ARGUMENT;
+    EpilogueParams ep{};
+    ep.out = mat_d;
+    ep.ld = ld_d;
+    ep.a_add = static_cast<const int32_t*>(vec_a_add);
+    ep.b_add = static_cast<const int32_t*>(vec_b_add);
+    ep.a_mul = static_cast<const __nv_bfloat16*>(vec_a_mul);
+    ep.b_mul = static_cast<const __nv_bfloat16*>(vec_b_mul);
+    return run_gemm(true, ep, mat_a, mat_b, M, K, N, stream);
+}
+
+extern "C" int fused_matmul_dequantize_int4_int4t_bf16_cuda(void* mat_d, const void* mat_a, const void* mat_b,
+                                                            const void* vec_a_add, const void* vec_b_add,
+                                                            const void* vec_a_mul, const void* vec_b_mul, int M, int K,
+                                                            int N, cudaStream_t stream) {
+    return fused_matmul_dequantize_int4_int4t_bf16_strided_cuda(mat_d, (long long)N, mat_a, mat_b, vec_a_add, vec_b_add,
+                                                                vec_a_mul, vec_b_mul, M, K, N, stream);
+}
+
+extern "C" int quest_b200_device_status(int* status) {
+    if (status == nullptr) return QB200_ERR_INVALID_ARGUMENT;
+    if (cudaDeviceSynchronize() != cudaSuccess) return QB200_ERR_CUDA;
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)) != cudaSuccess) return QB200_ERR_CUDA;
+    if (v != 0) {
+        const int zero = 0;
+        if (cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int)) != cudaSuccess) return QB200_ERR_CUDA;
+    }
+    *status = v;
+    return QB200_OK;
+}
+
+extern "C" const char* quest_b200_error_string(int status) {
+    switch (status & 0xFF) {
+        case QB200_OK: return "ok";
+        case QB200_ERR_INVALID_ARGUMENT: return "invalid argument (null pointer, negative size or misaligned buffer)";
+        case QB200_ERR_UNSUPPORTED: return "shape not supported by the sm_100a kernels";
+        case QB200_ERR_CUDA: return "CUDA runtime call or kernel launch failed";
+        case QB200_ERR_DRIVER: return "cuTensorMapEncodeTiled unavailable or failed";
+        case QB200_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel timed out";
+        default: return "unknown status";
+    }
+}
+
+extern "C" int quest_b200_version(void) { return 100; }

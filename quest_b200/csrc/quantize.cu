@@ -1,0 +1,526 @@
+// Row-wise kernels of the W4A4 linear path for sm_100a:
+//   - fused block-Hadamard + RMS scale + int4 quantise + pack + row-sum (one pass over x),
+//   - the reference's unfused find_scale_int4 / quantize_int4 (same kernel, other template arms),
+//   - add_mul_vv (the exact dequantising epilogue as a standalone kernel).
+//
+// All of them are HBM-bandwidth bound.  One thread block owns one row; every lane owns runs of 32
+// contiguous elements (four 16-byte loads, one 16-byte packed store), a "unit" being the 1024
+// elements a warp covers at once.  The whole row stays in registers (as bf16 pairs) between the
+// sum-of-squares pass and the quantise pass, so x is read from HBM exactly once.
+//
+// Numerics follow gemm-quest/quest/quantize_kernel.cu and gemm-quest/benchmarks/utils.py:
+//   two rounding points decide the codes - the Hadamard output is rounded to bf16 before anything
+//   else looks at it, and the scale is rounded to bf16 before the divide.
+#include "common.cuh"
+
+namespace qb {
+
+struct RowParams {
+    const __nv_bfloat16* x;        // [M,K] input
+    __nv_bfloat16* x_out;          // optional [M,K] output (transformed or dequantised values)
+    const __nv_bfloat16* scale_in; // optional [M] scale to quantise with
+    __nv_bfloat16* scale_out;      // optional [M] computed scale
+    int8_t* q_dense;               // optional [M,K]
+    uint8_t* q_packed;             // optional [M,K/2]
+    int32_t* row_sum;              // optional [M]
+    int K;
+    int M;
+    float had_scale;               // Hadamard normalisation constant
+    int x_out_mode;                // 0 none, 1 transformed values, 2 dequantised values
+    int quantize;                  // 0: stop after the scale (find_scale / transform only)
+};
+
+constexpr int kUnit = 1024;        // elements per warp-unit
+constexpr int kMaxVectorK = 64 * kUnit;  // 16 warps x 4 units; longer rows take the scalar kernel
+constexpr float kFloorMagic = 12582912.0f;  // 1.5 * 2^23: adding it (round-down) leaves floor(y) in the low mantissa bits
+constexpr int kFloorMagicBits = 0x4B400000;
+
+// floor(x / s) for bf16-valued x and s, without a divide.
+//
+// x / s is an exact integer for about 1 % of the elements, so a plain x * (1/s) mis-floors.  For
+// bf16 operands every non-integer quotient of magnitude <= 8 is at least 2^-9 away from an integer,
+// while x * rcp(s) is within 2^-22 relative of the true quotient; nudging the product by
+// |y| * 2^-13 towards +inf therefore lands exact integers on or above themselves and moves nothing
+// else across an integer (and keeps the sign of tiny quotients, so -tiny still floors to -1).
+// Verified exhaustively over all pairs of bf16 mantissas and the exponent differences that matter.
+// Returns floor as an int; out-of-range quotients keep their sign and saturate later.
+__device__ __forceinline__ int floor_quotient(float x, float inv_s) {
+    const float y = x * inv_s;
+    const float y2 = fmaf(fabsf(y), 1.220703125e-4f, y);
+    return __float_as_int(__fadd_rd(y2, kFloorMagic)) - kFloorMagicBits;
+}
+
+// (sat4(a) << 4 | sat4(b)) | (c << 8): saturating pack of two int32 to signed nibbles.
+__device__ __forceinline__ uint32_t pack_sat_s4(int hi, int lo, uint32_t c) {
+    uint32_t d;
+    asm("cvt.pack.sat.s4.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(hi), "r"(lo), "r"(c));
+    return d;
+}
+
+// Sum of the eight signed nibbles of w, times 16, accumulated into acc.
+__device__ __forceinline__ int nibble_sum16(uint32_t w, int acc) {
+    const uint32_t lo = (w << 4) & 0xF0F0F0F0u;
+    const uint32_t hi = w & 0xF0F0F0F0u;
+    acc = __dp4a((int)lo, 0x01010101, acc);
+    acc = __dp4a((int)hi, 0x01010101, acc);
+    return acc;
+}
+
+template <int HB>
+__device__ __forceinline__ void hadamard32(float (&f)[32], int lane) {
+    // Index bits 0..4 live in registers.
+#pragma unroll
+    for (int s = 1; s < 32; s <<= 1) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            if ((i & s) == 0) {
+                const float a = f[i], b = f[i + s];
+                f[i] = a + b;
+                f[i + s] = a - b;
+            }
+        }
+    }
+    // The remaining log2(HB/32) index bits are lane bits: butterfly through warp shuffles.
+#pragma unroll
+    for (int m = 1; m < HB / 32; m <<= 1) {
+        const float sgn = (lane & m) ? -1.f : 1.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            const float p = __shfl_xor_sync(0xffffffffu, f[i], m);
+            f[i] = fmaf(f[i], sgn, p);  // lower lane: a + b, upper lane: a - b
+        }
+    }
+}
+
+// HB: Hadamard block (0 = none).  UNITS: 1024-element units per warp.  EXTRAS: compile the rarely
+// used outputs (dense int8 codes, transformed / dequantised bf16 values).
+template <int HB, int UNITS, bool EXTRAS>
+__global__ void __launch_bounds__(UNITS == 1 ? 256 : 512) row_kernel(const RowParams p) {
+    const int row = blockIdx.x;
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int nwarps = blockDim.x >> 5;
+    const int K = p.K;
+    const __nv_bfloat16* xr = p.x + (size_t)row * K;
+
+    __shared__ double red_f[32];
+    __shared__ int red_i[32];
+
+    uint32_t v[UNITS][16];  // the lane's elements as bf16 pairs, after the transform
+    float ssq = 0.f;
+
+    // Issue every load of the row before touching the data.
+    uint4 raw[UNITS][4];
+#pragma unroll
+    for (int u = 0; u < UNITS; ++u) {
+        const int e0 = (u * nwarps + warp) * kUnit + lane * 32;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            raw[u][j] = make_uint4(0, 0, 0, 0);
+            if (e0 + 8 * j < K) {
+                // The EXTRAS arms may write x in place, so they use ordinary (coherent) loads.
+                if (EXTRAS) raw[u][j] = *reinterpret_cast<const uint4*>(xr + e0 + 8 * j);
+                else raw[u][j] = ld_stream16(xr + e0 + 8 * j);
+            }
+        }
+    }
+
+#pragma unroll
+    for (int u = 0; u < UNITS; ++u) {
+        const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw[u][0]);
+        if (HB > 0) {
+            float f[32];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                f[2 * i] = bf16lo_to_f32(w[i]);
+                f[2 * i + 1] = bf16hi_to_f32(w[i]);
+            }
+            hadamard32<HB>(f, lane);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[u][i] = pack_bf16x2(f[2 * i] * p.had_scale, f[2 * i + 1] * p.had_scale);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[u][i] = w[i];
+        }
+        if (p.scale_in == nullptr) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float a = bf16lo_to_f32(v[u][i]), b = bf16hi_to_f32(v[u][i]);
+                ssq = fmaf(a, a, ssq);
+                ssq = fmaf(b, b, ssq);
+            }
+        }
+    }
+
+    // ---- scale ----
+    float s;
+    if (p.scale_in != nullptr) {
+        s = bf16_to_f32(p.scale_in[row]);
+    } else {
+        double t = (double)ssq;
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) t += __shfl_xor_sync(0xffffffffu, t, m);
+        if (lane == 0) red_f[warp] = t;
+        __syncthreads();
+        double tot = 0.0;
+        for (int i = 0; i < nwarps; ++i) tot += red_f[i];
+        const float mean_sq = (float)(tot / (double)K);
+        const __nv_bfloat16 sb = __float2bfloat16_rn(quest_scale_from_mean_square(mean_sq));
+        if (threadIdx.x == 0 && p.scale_out != nullptr) p.scale_out[row] = sb;
+        s = bf16_to_f32(sb);
+    }
+
+    if (EXTRAS && p.x_out_mode == 1) {
+#pragma unroll
+        for (int u = 0; u < UNITS; ++u) {
+            const int e0 = (u * nwarps + warp) * kUnit + lane * 32;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (e0 + 8 * j < K)
+                    *reinterpret_cast<uint4*>(p.x_out + (size_t)row * K + e0 + 8 * j) =
+                        make_uint4(v[u][4 * j], v[u][4 * j + 1], v[u][4 * j + 2], v[u][4 * j + 3]);
+        }
+    }
+    if (!p.quantize) return;
+
+    // ---- quantise, pack, row sum ----
+    const float inv_s = __frcp_rn(s);
+    const bool vec_store = (K & 31) == 0;
+    int rs16 = 0;
+#pragma unroll
+    for (int u = 0; u < UNITS; ++u) {
+        const int e0 = (u * nwarps + warp) * kUnit + lane * 32;
+        uint32_t pk[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            int q[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                q[2 * i] = floor_quotient(bf16lo_to_f32(v[u][4 * j + i]), inv_s);
+                q[2 * i + 1] = floor_quotient(bf16hi_to_f32(v[u][4 * j + i]), inv_s);
+            }
+            uint32_t d = pack_sat_s4(q[7], q[6], 0u);
+            d = pack_sat_s4(q[5], q[4], d);
+            d = pack_sat_s4(q[3], q[2], d);
+            d = pack_sat_s4(q[1], q[0], d);
+            pk[j] = d;
+            rs16 = nibble_sum16(d, rs16);  // padding lanes hold zeros: code 0, adds nothing
+
+            if (EXTRAS && e0 + 8 * j < K) {
+                if (p.q_dense != nullptr) {
+                    uint32_t lo = 0, hi = 0;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        lo |= (uint32_t)(min(max(q[i], -8), 7) & 0xFF) << (8 * i);
+                        hi |= (uint32_t)(min(max(q[4 + i], -8), 7) & 0xFF) << (8 * i);
+                    }
+                    *reinterpret_cast<uint2*>(p.q_dense + (size_t)row * K + e0 + 8 * j) = make_uint2(lo, hi);
+                }
+                if (p.x_out_mode == 2) {
+                    uint32_t o[4];
+                    const float half_s = s * 0.5f;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float a = fmaf((float)min(max(q[2 * i], -8), 7), s, half_s);
+                        const float b = fmaf((float)min(max(q[2 * i + 1], -8), 7), s, half_s);
+                        o[i] = pack_bf16x2(a, b);
+                    }
+                    *reinterpret_cast<uint4*>(p.x_out + (size_t)row * K + e0 + 8 * j) =
+                        make_uint4(o[0], o[1], o[2], o[3]);
+                }
+            }
+        }
+        if (p.q_packed != nullptr) {
+            uint8_t* dst = p.q_packed + (size_t)row * (K >> 1) + (e0 >> 1);
+            if (vec_store) {
+                if (e0 < K) *reinterpret_cast<uint4*>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (e0 + 8 * j < K) *reinterpret_cast<uint32_t*>(dst + 4 * j) = pk[j];
+            }
+        }
+    }
+    if (p.row_sum != nullptr) {
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) rs16 += __shfl_xor_sync(0xffffffffu, rs16, m);
+        if (lane == 0) red_i[warp] = rs16;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int tot = 0;
+            for (int i = 0; i < nwarps; ++i) tot += red_i[i];
+            p.row_sum[row] = tot >> 4;  // exact: every term is a multiple of 16
+        }
+    }
+}
+
+// Any K, any alignment, no Hadamard: one block per row, scalar accesses.  Only used for shapes the
+// vector kernel does not cover (K not a multiple of 8, misaligned base pointers, K > 65536).
+__global__ void __launch_bounds__(256) row_kernel_generic(const RowParams p) {
+    const int row = blockIdx.x;
+    const int K = p.K;
+    const __nv_bfloat16* xr = p.x + (size_t)row * K;
+    __shared__ double red_f[8];
+    __shared__ int red_i[8];
+    __shared__ float s_sh;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float s;
+    if (p.scale_in != nullptr) {
+        s = bf16_to_f32(p.scale_in[row]);
+    } else {
+        double t = 0.0;
+        for (int k = threadIdx.x; k < K; k += blockDim.x) {
+            const float a = bf16_to_f32(xr[k]);
+            t += (double)(a * a);
+        }
+        for (int m = 16; m > 0; m >>= 1) t += __shfl_xor_sync(0xffffffffu, t, m);
+        if (lane == 0) red_f[warp] = t;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            double tot = 0.0;
+            for (int i = 0; i < 8; ++i) tot += red_f[i];
+            const __nv_bfloat16 sb = __float2bfloat16_rn(quest_scale_from_mean_square((float)(tot / (double)K)));
+            if (p.scale_out != nullptr) p.scale_out[row] = sb;
+            s_sh = bf16_to_f32(sb);
+        }
+        __syncthreads();
+        s = s_sh;
+    }
+    if (!p.quantize) return;
+    const float inv_s = __frcp_rn(s);
+    int rs = 0;
+    // Each thread owns pairs of columns so that it can emit whole packed bytes.
+    for (int k = 2 * threadIdx.x; k < K; k += 2 * blockDim.x) {
+        int q[2] = {0, 0};
+        for (int i = 0; i < 2; ++i) {
+            if (k + i < K) {
+                q[i] = min(max(floor_quotient(bf16_to_f32(xr[k + i]), inv_s), -8), 7);
+                rs += q[i];
+                if (p.q_dense != nullptr) p.q_dense[(size_t)row * K + k + i] = (int8_t)q[i];
+                if (p.x_out_mode == 2)
+                    p.x_out[(size_t)row * K + k + i] = __float2bfloat16_rn(fmaf((float)q[i], s, s * 0.5f));
+            }
+        }
+        if (p.q_packed != nullptr && k + 1 < K)
+            p.q_packed[(size_t)row * (K >> 1) + (k >> 1)] = (uint8_t)((q[1] << 4) | (q[0] & 0xF));
+    }
+    if (p.row_sum != nullptr) {
+        for (int m = 16; m > 0; m >>= 1) rs += __shfl_xor_sync(0xffffffffu, rs, m);
+        if (lane == 0) red_i[warp] = rs;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int tot = 0;
+            for (int i = 0; i < 8; ++i) tot += red_i[i];
+            p.row_sum[row] = tot;
+        }
+    }
+}
+
+template <int HB, bool EXTRAS>
+static int launch_row(const RowParams& p, cudaStream_t stream) {
+    const int units = (p.K + kUnit - 1) / kUnit;
+    const dim3 grid((unsigned)p.M);
+    if (units <= 8) {
+        row_kernel<HB, 1, EXTRAS><<<grid, 32 * units, 0, stream>>>(p);
+    } else if (units <= 32) {
+        row_kernel<HB, 2, EXTRAS><<<grid, 32 * ((units + 1) / 2), 0, stream>>>(p);
+    } else if (units <= 64) {
+        row_kernel<HB, 4, EXTRAS><<<grid, 32 * ((units + 3) / 4), 0, stream>>>(p);
+    } else {
+        return QB200_ERR_UNSUPPORTED;
+    }
+    return launch_status();
+}
+
+static bool vector_path_ok(const RowParams& p) {
+    if (p.K % 8 != 0 || p.K > kMaxVectorK) return false;
+    if (!aligned16(p.x)) return false;
+    if (p.x_out != nullptr && !aligned16(p.x_out)) return false;
+    if (p.q_dense != nullptr && (reinterpret_cast<uintptr_t>(p.q_dense) & 7u)) return false;
+    if (p.q_packed != nullptr && !aligned16(p.q_packed)) return false;
+    return true;
+}
+
+static int run_rows(const RowParams& p, int block, bool extras, cudaStream_t stream) {
+    if (p.M == 0 || p.K == 0) return QB200_OK;
+    if (!vector_path_ok(p)) {
+        if (block != 0) return QB200_ERR_UNSUPPORTED;
+        row_kernel_generic<<<(unsigned)p.M, 256, 0, stream>>>(p);
+        return launch_status();
+    }
+    switch (block) {
+        case 0: return extras ? launch_row<0, true>(p, stream) : launch_row<0, false>(p, stream);
+        case 64: return extras ? launch_row<64, true>(p, stream) : launch_row<64, false>(p, stream);
+        case 128: return extras ? launch_row<128, true>(p, stream) : launch_row<128, false>(p, stream);
+        case 256: return extras ? launch_row<256, true>(p, stream) : launch_row<256, false>(p, stream);
+        default: return QB200_ERR_UNSUPPORTED;
+    }
+}
+
+// -------------------------------------------------------------------------------------------------
+// add_mul_vv: D = bf16( float(2C + a_add[m] + b_add[n]) * (0.5f * a_mul[m] * b_mul[n]) )
+// 6 bytes per element of HBM traffic; eight columns per thread when N allows 16-byte accesses.
+// -------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float dequant_one(int c, int a_add, int b_add, float a_mul, float b_mul) {
+    const float lhs = (float)(c * 2 + a_add + b_add);
+    const float rhs = 0.5f * a_mul * b_mul;
+    return lhs * rhs;
+}
+
+__global__ void __launch_bounds__(256) add_mul_vv_vec8_kernel(__nv_bfloat16* __restrict__ d,
+                                                              const int32_t* __restrict__ a_add,
+                                                              const __nv_bfloat16* __restrict__ a_mul,
+                                                              const int32_t* __restrict__ b_add,
+                                                              const __nv_bfloat16* __restrict__ b_mul,
+                                                              const int32_t* __restrict__ c, int M, int N) {
+    const int groups_per_row = N >> 3;
+    const long long total = (long long)M * groups_per_row;
+    for (long long g = blockIdx.x * (long long)blockDim.x + threadIdx.x; g < total;
+         g += (long long)gridDim.x * blockDim.x) {
+        const int row = (int)(g / groups_per_row);
+        const int col = (int)(g - (long long)row * groups_per_row) << 3;
+        const int aa = a_add[row];
+        const float am = bf16_to_f32(a_mul[row]);
+        const int4 c0 = *reinterpret_cast<const int4*>(c + (size_t)row * N + col);
+        const int4 c1 = *reinterpret_cast<const int4*>(c + (size_t)row * N + col + 4);
+        const int4 b0 = *reinterpret_cast<const int4*>(b_add + col);
+        const int4 b1 = *reinterpret_cast<const int4*>(b_add + col + 4);
+        const uint4 bm = *reinterpret_cast<const uint4*>(b_mul + col);
+        uint4 o;
+        o.x = pack_bf16x2(dequant_one(c0.x, aa, b0.x, am, bf16lo_to_f32(bm.x)),
+                          dequant_one(c0.y, aa, b0.y, am, bf16hi_to_f32(bm.x)));
+        o.y = pack_bf16x2(dequant_one(c0.z, aa, b0.z, am, bf16lo_to_f32(bm.y)),
+                          dequant_one(c0.w, aa, b0.w, am, bf16hi_to_f32(bm.y)));
+        o.z = pack_bf16x2(dequant_one(c1.x, aa, b1.x, am, bf16lo_to_f32(bm.z)),
+                          dequant_one(c1.y, aa, b1.y, am, bf16hi_to_f32(bm.z)));
+        o.w = pack_bf16x2(dequant_one(c1.z, aa, b1.z, am, bf16lo_to_f32(bm.w)),
+                          dequant_one(c1.w, aa, b1.w, am, bf16hi_to_f32(bm.w)));
+        *reinterpret_cast<uint4*>(d + (size_t)row * N + col) = o;
+    }
+}
+
+__global__ void __launch_bounds__(256) add_mul_vv_scalar_kernel(__nv_bfloat16* __restrict__ d,
+                                                                const int32_t* __restrict__ a_add,
+                                                                const __nv_bfloat16* __restrict__ a_mul,
+                                                                const int32_t* __restrict__ b_add,
+                                                                const __nv_bfloat16* __restrict__ b_mul,
+                                                                const int32_t* __restrict__ c, int M, int N) {
+    const long long total = (long long)M * N;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int row = (int)(i / N);
+        const int col = (int)(i - (long long)row * N);
+        d[i] = __float2bfloat16_rn(
+            dequant_one(c[i], a_add[row], b_add[col], bf16_to_f32(a_mul[row]), bf16_to_f32(b_mul[col])));
+    }
+}
+
+}  // namespace qb
+
+// -------------------------------------------------------------------------------------------------
+// C ABI
+// -------------------------------------------------------------------------------------------------
+using namespace qb;
+
+extern "C" int find_scale_int4_cuda_bf16(void* scale_ptr, const void* x_ptr, int group_size, int batch_size,
+                                         cudaStream_t stream) {
+    if (group_size < 0 || batch_size < 0) return QB200_ERR_INVALID_ARGUMENT;
+    if (batch_size == 0) return QB200_OK;
+    if (scale_ptr == nullptr || x_ptr == nullptr || group_size == 0) return QB200_ERR_INVALID_ARGUMENT;
+    RowParams p{};
+    p.x = static_cast<const __nv_bfloat16*>(x_ptr);
+    p.scale_out = static_cast<__nv_bfloat16*>(scale_ptr);
+    p.K = group_size;
+    p.M = batch_size;
+    p.quantize = 0;
+    return run_rows(p, 0, false, stream);
+}
+
+extern "C" int quantize_int4_cuda_bf16(void* x_ptr, const void* scale_ptr, void* x_int_ptr, void* x_int_packed_ptr,
+                                       void* x_int_row_sum_ptr, int group_size, int batch_size, int do_dequantize,
+                                       cudaStream_t stream) {
+    if (group_size < 0 || batch_size < 0) return QB200_ERR_INVALID_ARGUMENT;
+    if (batch_size == 0 || group_size == 0) return QB200_OK;
+    if (x_ptr == nullptr || scale_ptr == nullptr) return QB200_ERR_INVALID_ARGUMENT;
+    if (x_int_packed_ptr != nullptr && (group_size & 1)) return QB200_ERR_INVALID_ARGUMENT;
+    RowParams p{};
+    p.x = static_cast<const __nv_bfloat16*>(x_ptr);
+    p.scale_in = static_cast<const __nv_bfloat16*>(scale_ptr);
+    p.q_dense = static_cast<int8_t*>(x_int_ptr);
+    p.q_packed = static_cast<uint8_t*>(x_int_packed_ptr);
+    p.row_sum = static_cast<int32_t*>(x_int_row_sum_ptr);
+    p.K = group_size;
+    p.M = batch_size;
+    p.quantize = 1;
+    if (do_dequantize) {
+        p.x_out = static_cast<__nv_bfloat16*>(x_ptr);
+        p.x_out_mode = 2;
+    }
+    const bool extras = do_dequantize || x_int_ptr != nullptr;
+    return run_rows(p, 0, extras, stream);
+}
+
+extern "C" int hadamard_quantize_int4_cuda_bf16(void* x_int_packed_ptr, void* scale_ptr, void* x_int_row_sum_ptr,
+                                                const void* x_ptr, int group_size, int batch_size, int block,
+                                                cudaStream_t stream) {
+    if (group_size < 0 || batch_size < 0) return QB200_ERR_INVALID_ARGUMENT;
+    if (block != 64 && block != 128 && block != 256) return QB200_ERR_UNSUPPORTED;
+    if (batch_size == 0) return QB200_OK;
+    if (x_int_packed_ptr == nullptr || scale_ptr == nullptr || x_ptr == nullptr || group_size == 0)
+        return QB200_ERR_INVALID_ARGUMENT;
+    if (group_size % block != 0) return QB200_ERR_INVALID_ARGUMENT;
+    RowParams p{};
+    p.x = static_cast<const __nv_bfloat16*>(x_ptr);
+    p.scale_out = static_cast<__nv_bfloat16*>(scale_ptr);
+    p.q_packed = static_cast<uint8_t*>(x_int_packed_ptr);
+    p.row_sum = static_cast<int32_t*>(x_int_row_sum_ptr);
+    p.K = group_size;
+    p.M = batch_size;
+    p.quantize = 1;
+    p.had_scale = __bfloat162float(__float2bfloat16_rn((float)(1.0 / sqrt((double)block))));
+    return run_rows(p, block, false, stream);
+}
+
+extern "C" int hadamard_transform_cuda_bf16(void* out_ptr, const void* x_ptr, int group_size, int batch_size,
+                                            int block, int weight_side, cudaStream_t stream) {
+    if (group_size < 0 || batch_size < 0) return QB200_ERR_INVALID_ARGUMENT;
+    if (block != 64 && block != 128 && block != 256) return QB200_ERR_UNSUPPORTED;
+    if (batch_size == 0) return QB200_OK;
+    if (out_ptr == nullptr || x_ptr == nullptr || group_size == 0 || group_size % block != 0)
+        return QB200_ERR_INVALID_ARGUMENT;
+    RowParams p{};
+    p.x = static_cast<const __nv_bfloat16*>(x_ptr);
+    p.x_out = static_cast<__nv_bfloat16*>(out_ptr);
+    p.x_out_mode = 1;
+    p.K = group_size;
+    p.M = batch_size;
+    p.quantize = 0;
+    const float exact = (float)(1.0 / sqrt((double)block));  // fp32 rounding of block^-0.5
+    p.had_scale = weight_side ? exact : __bfloat162float(__float2bfloat16_rn(exact));
+    return run_rows(p, block, true, stream);
+}
+
+extern "C" int add_mul_vv_cuda_bf16(void* mat_d, const void* vec_a_add, const void* vec_a_mul, const void* vec_b_add,
+                                    const void* vec_b_mul, const void* mat_c, int size_a, int size_b,
+                                    cudaStream_t stream) {
+    if (size_a < 0 || size_b < 0) return QB200_ERR_INVALID_ARGUMENT;
+    if (size_a == 0 || size_b == 0) return QB200_OK;
+    if (!mat_d || !vec_a_add || !vec_a_mul || !vec_b_add || !vec_b_mul || !mat_c) return QB200_ERR_INVALID_ARGUMENT;
+    auto* d = static_cast<__nv_bfloat16*>(mat_d);
+    auto* aa = static_cast<const int32_t*>(vec_a_add);
+    auto* am = static_cast<const __nv_bfloat16*>(vec_a_mul);
+    auto* ba = static_cast<const int32_t*>(vec_b_add);
+    auto* bm = static_cast<const __nv_bfloat16*>(vec_b_mul);
+    auto* c = static_cast<const int32_t*>(mat_c);
+    const long long total = (long long)size_a * size_b;
+    const bool vec = (size_b % 8 == 0) && aligned16(d) && aligned16(c) && aligned16(ba) && aligned16(bm);
+    const long long work = vec ? total / 8 : total;
+    long long blocks = (work + 255) / 256;
+    const long long cap = 148LL * 8 * 4;  // grid-stride beyond a few waves of the 148 SMs
+    if (blocks > cap) blocks = cap;
+    if (vec)
+        add_mul_vv_vec8_kernel<<<(unsigned)blocks, 256, 0, stream>>>(d, aa, am, ba, bm, c, size_a, size_b);
+    else
+        add_mul_vv_scalar_kernel<<<(unsigned)blocks, 256, 0, stream>>>(d, aa, am, ba, bm, c, size_a, size_b);
+    return launch_status();
+}

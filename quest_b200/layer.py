@@ -1,0 +1,138 @@
+"""Layer logic on top of the ops: weight preparation, the W4A4 linear forward and the module.
+
+Mirrors the dense branches of gemm-quest/benchmarks/utils.py (``preprocess_weight`` :20-53,
+``linear_forward`` :56-111, ``unpack_int4`` :420-445) and ``Linear4bit`` of
+gemm-quest/benchmarks/bench_e2e.py:41-70, without the backend switch (there is one backend) and without
+the 4:8-sparse branch.  With ``use_hadamard`` the activation side is ONE fused kernel
+(Hadamard + scale + quantise + pack + row sum) followed by the fused GEMM: two launches per layer
+instead of the reference's four.
+"""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+import quest_b200 as quest
+
+HADAMARD_BLOCK = 128  # the reference hard-codes block 128 (utils.py:17, 39, 90)
+
+
+def preprocess_weight(
+        weight: torch.Tensor,
+        use_sparse: bool = False,
+        use_hadamard: bool = False,
+        backend: str = 'cuda',
+        block: int = HADAMARD_BLOCK,
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor | None]:
+    """weight bf16 (N, K) -> (w_int_packed u8 (N, K//2), w_scale bf16 (N, 1), w_add i32 (N, 1), None).
+
+    ``w_add = row_sum + K // 2`` folds the +0.5 offsets of both operands into the epilogue
+    (utils.py:48).  ``backend`` is accepted for signature compatibility and ignored.
+    """
+    if use_sparse:
+        raise NotImplementedError("quest_b200 implements the dense W4A4 path only")
+    weight = weight.contiguous()
+    if use_hadamard:
+        weight = quest.hadamard_transform(weight, block=block, weight_side=True)
+    N, K = weight.shape
+    w_scale = torch.empty(N, 1, dtype=weight.dtype, device=weight.device)
+    w_int_packed = torch.empty(N, K // 2, dtype=torch.uint8, device=weight.device)
+    w_int_row_sum = torch.empty(N, 1, dtype=torch.int32, device=weight.device)
+    quest.find_scale_int4(x=weight, scale=w_scale)
+    quest.quantize_int4(x=weight, scale=w_scale, x_int=None, x_int_packed=w_int_packed,
+                        x_int_row_sum=w_int_row_sum, do_dequantize=False)
+    w_add = w_int_row_sum + K // 2
+    return w_int_packed, w_scale, w_add, None
+
+
+def linear_forward(
+        activation: torch.Tensor,
+        w_int_packed: torch.Tensor,
+        w_scale: torch.Tensor,
+        w_add: torch.Tensor,
+        w_meta_e: torch.Tensor = None,
+        out: torch.Tensor = None,
+        _a_scale: torch.Tensor = None,
+        _a_int_packed: torch.Tensor = None,
+        _a_int_row_sum: torch.Tensor = None,
+        _c: torch.Tensor = None,
+        use_hadamard: bool = False,
+        backend: str = 'cuda',
+        block: int = HADAMARD_BLOCK,
+) -> torch.Tensor:
+    """out (M, N) bf16 = activation (M, K) @ weight^T in W4A4.  The ``_a_*`` arguments are optional
+    caller-owned workspaces (CUDA-graph friendly), as in the reference.  ``_c``, if given, makes the
+    call take the unfused int32 GEMM + add_mul_vv route (the reference's debug mode)."""
+    if w_meta_e is not None:
+        raise NotImplementedError("quest_b200 implements the dense W4A4 path only")
+    M, K, N = activation.size(0), activation.size(1), w_int_packed.size(0)
+    dtype, device = activation.dtype, activation.device
+    if out is None:
+        out = torch.empty(M, N, dtype=dtype, device=device)
+    a_scale = torch.empty(M, 1, dtype=dtype, device=device) if _a_scale is None else _a_scale
+    a_int_packed = torch.empty(M, K // 2, dtype=torch.uint8, device=device) if _a_int_packed is None else _a_int_packed
+    a_int_row_sum = torch.empty(M, 1, dtype=torch.int32, device=device) if _a_int_row_sum is None else _a_int_row_sum
+    if use_hadamard:
+        quest.hadamard_quantize_int4(activation, block=block, x_int_packed=a_int_packed, scale=a_scale,
+                                     x_int_row_sum=a_int_row_sum)
+    else:
+        quest.find_scale_int4(x=activation, scale=a_scale)
+        quest.quantize_int4(x=activation, scale=a_scale, x_int=None, x_int_packed=a_int_packed,
+                            x_int_row_sum=a_int_row_sum, do_dequantize=False)
+    if _c is not None:
+        quest.matmul_int4_int4t_int32(mat_a=a_int_packed, mat_b=w_int_packed, out=_c)
+        quest.add_mul_vv(vec_a_add=a_int_row_sum, vec_a_mul=a_scale, vec_b_add=w_add, vec_b_mul=w_scale,
+                         mat_c=_c, mat_d=out)
+    else:
+        quest.fused_matmul_dequantize_int4_int4t_bf16(mat_a=a_int_packed, mat_b=w_int_packed,
+                                                      vec_a_add=a_int_row_sum, vec_b_add=w_add,
+                                                      vec_a_mul=a_scale, vec_b_mul=w_scale, out=out)
+    return out
+
+
+def unpack_int4(x_int_packed: torch.Tensor) -> torch.Tensor:
+    """uint8 (..., K // 2) -> int8 codes (..., K); test helper, plain torch (utils.py:420-445)."""
+    x_int = torch.empty(*x_int_packed.shape[:-1], x_int_packed.size(-1) * 2, dtype=torch.int8,
+                        device=x_int_packed.device)
+    x_int[..., ::2] = x_int_packed & 0xF
+    x_int[..., 1::2] = x_int_packed >> 4
+    return torch.where(x_int >= 8, x_int - 16, x_int)
+
+
+class Linear4bit(nn.Module):
+    """nn.Linear whose weight is stored as packed int4 + per-row scale/offset and whose forward runs
+    the W4A4 kernels (gemm-quest/benchmarks/bench_e2e.py:41-70).  Needs a CUDA device."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = True, device=None, dtype=None,
+                 use_sparse: bool = False, use_hadamard: bool = False, use_noop: bool = False,
+                 weight: torch.Tensor | None = None):
+        super().__init__()
+        self.in_features, self.out_features = in_features, out_features
+        self.use_hadamard: bool = use_hadamard
+        self.use_noop: bool = use_noop
+        nn_linear = nn.Linear(in_features, out_features, bias=bias, device=device, dtype=dtype)
+        if weight is not None:
+            nn_linear.weight.data.copy_(weight)
+        self.bias = nn_linear.bias
+        w = nn_linear.weight.data
+        self.weight = torch.empty_like(w, device=torch.device('meta'))
+        w_int_packed, w_scale, w_add, w_meta_e = preprocess_weight(weight=w, use_sparse=use_sparse,
+                                                                   use_hadamard=use_hadamard)
+        self.register_buffer('w_int_packed', w_int_packed)
+        self.register_buffer('w_scale', w_scale)
+        self.register_buffer('w_add', w_add)
+        self.register_buffer('w_meta_e', w_meta_e)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if not self.use_noop:
+            a = x.contiguous().flatten(end_dim=-2)
+            y = linear_forward(activation=a, w_int_packed=self.w_int_packed, w_scale=self.w_scale, w_add=self.w_add,
+                               w_meta_e=self.w_meta_e, out=None, use_hadamard=self.use_hadamard)
+            y = y.unflatten(dim=0, sizes=x.shape[:-1])
+        else:
+            if self.use_hadamard:
+                x = quest.hadamard_transform(x.contiguous(), block=HADAMARD_BLOCK, weight_side=True)
+            y = torch.zeros(*x.shape[:-1], self.out_features, dtype=x.dtype, device=x.device)
+        if self.bias is not None:
+            y += self.bias
+        return y

@@ -1,0 +1,360 @@
+"""GPU parity tests: every op goes through the C-ABI library and is compared with the CPU oracle on the
+same seeded inputs.  Integer outputs (codes, packed bytes, row sums, int32 accumulators) must be bit-exact;
+bf16 outputs of the epilogue must be bit-exact given exact accumulators.  The only tolerated deviation is
+the documented one for the Hadamard step: +-1 code flips at rounding ties (rate asserted below)."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+from oracle import quest_oracle as O
+from conftest import GOLDEN_CASES, load_golden, make_activations
+
+pytestmark = pytest.mark.gpu
+
+if torch.cuda.is_available():
+    import quest_b200 as quest
+    DEV = torch.device("cuda:0")
+
+
+@pytest.fixture(autouse=True)
+def _device_status_clean():
+    yield
+    assert quest.device_status() == 0, "a kernel reported a bounded-wait timeout"
+
+
+def random_packed(rows: int, k: int, seed: int, lo: int = -8, hi: int = 7) -> torch.Tensor:
+    g = torch.Generator().manual_seed(seed)
+    codes = torch.randint(lo, hi + 1, (rows, k), generator=g, dtype=torch.int8)
+    return O.pack_int4(codes)
+
+
+# ------------------------------------------------------------------ scale / quantize ------------------
+@pytest.mark.parametrize("case", GOLDEN_CASES)
+def test_scale_and_quantize_match_reference_golden(case):
+    gd = load_golden(case)
+    for tag, key in (("a", "activation"), ("w", "weight")):
+        x = gd[key].to(DEV)
+        scale = quest.find_scale_int4(x)
+        assert scale.shape == (x.size(0), 1) and scale.dtype == torch.bfloat16
+        assert scale.cpu().equal(gd[f"{tag}_scale"])
+        x_int = torch.empty(x.shape, dtype=torch.int8, device=DEV)
+        packed = torch.empty(x.size(0), x.size(1) // 2, dtype=torch.uint8, device=DEV)
+        row_sum = torch.empty(x.size(0), 1, dtype=torch.int32, device=DEV)
+        xd = x.clone()
+        ret = quest.quantize_int4(xd, scale, x_int, packed, row_sum, do_dequantize=True)
+        assert ret[0] is xd and ret[1] is x_int and ret[2] is packed and ret[3] is row_sum
+        assert x_int.cpu().equal(gd[f"{tag}_int"])
+        assert packed.cpu().equal(gd[f"{tag}_int_packed"])
+        assert row_sum.cpu().equal(gd[f"{tag}_int_row_sum"])
+        assert xd.cpu().equal(gd[f"{tag}_dq"])
+        # None-output convention: absent outputs come back as None and x is untouched without dequantize
+        x2 = x.clone()
+        ret = quest.quantize_int4(x2, scale, x_int_packed=packed)
+        assert ret[1] is None and ret[3] is None and x2.equal(x)
+        assert packed.cpu().equal(gd[f"{tag}_int_packed"])
+        assert quest.unpack_int4(packed).cpu().equal(gd[f"{tag}_int"])
+
+
+@pytest.mark.parametrize("m", [1, 2, 17, 129])
+@pytest.mark.parametrize("k", [256, 776, 4096, 5632, 11008, 14336, 28672])
+def test_scale_and_quantize_shapes(m, k):
+    """K = 776 is not a multiple of 32 (4-byte packed stores); K > 8192 uses several units per warp."""
+    x = make_activations("outlier", m, k, seed=k + m)
+    x[0, : k // 2] = 0  # a half-empty row
+    if m > 1:
+        x[1] = 0        # an all-zero row: scale = bf16(1e-8), codes 0
+    xs = O.find_scale_int4(x)
+    p_ref = torch.empty(m, k // 2, dtype=torch.uint8)
+    r_ref = torch.empty(m, 1, dtype=torch.int32)
+    O.quantize_int4(x, xs, None, p_ref, r_ref)
+    xd = x.to(DEV)
+    scale = quest.find_scale_int4(xd)
+    mism = int((scale.cpu() != xs).sum())
+    assert mism == 0, f"{mism} scale mismatches"
+    _, _, packed, row_sum = quest.quantize_int4(xd, scale, None, torch.empty_like(p_ref, device=DEV),
+                                                torch.empty_like(r_ref, device=DEV))
+    assert packed.cpu().equal(p_ref)
+    assert row_sum.cpu().equal(r_ref)
+
+
+def test_quantize_generic_path_odd_shapes():
+    """K % 8 != 0 and a misaligned base pointer take the scalar kernel; results must not change."""
+    for k in (6, 100, 1022):
+        x = make_activations("randn", 5, k, seed=k)
+        xs = O.find_scale_int4(x)
+        xi = torch.empty(5, k, dtype=torch.int8)
+        p_ref = torch.empty(5, k // 2, dtype=torch.uint8)
+        r_ref = torch.empty(5, 1, dtype=torch.int32)
+        xq = x.clone()
+        O.quantize_int4(xq, xs, xi, p_ref, r_ref, True)
+        xd = x.to(DEV)
+        scale = quest.find_scale_int4(xd)
+        assert scale.cpu().equal(xs)
+        out = quest.quantize_int4(xd, scale, torch.empty_like(xi, device=DEV), torch.empty_like(p_ref, device=DEV),
+                                  torch.empty_like(r_ref, device=DEV), True)
+        assert out[0].cpu().equal(xq) and out[1].cpu().equal(xi) and out[2].cpu().equal(p_ref) and out[3].cpu().equal(r_ref)
+    # misaligned (but contiguous) view
+    base = make_activations("randn", 1, 4 * 256 + 8, seed=9).view(-1).to(DEV)
+    x = base[3:3 + 4 * 256].view(4, 256)
+    assert x.is_contiguous() and x.data_ptr() % 16 != 0
+    assert quest.find_scale_int4(x).cpu().equal(O.find_scale_int4(x.cpu()))
+
+
+def test_exact_integer_quotients_floor_correctly():
+    """x / scale is an exact integer for ~1 % of real data; build rows where it is for EVERY element."""
+    scale = torch.tensor([[0.3359375], [1.0], [3.0517578125e-05], [24.0]], dtype=torch.bfloat16)
+    n = torch.arange(-10, 10, dtype=torch.float32).repeat(13)[:256]
+    x = (n.view(1, -1) * scale.float()).to(torch.bfloat16)
+    assert ((x.float() / scale.float()) == n).all()
+    p_ref = torch.empty(4, 128, dtype=torch.uint8)
+    O.quantize_int4(x, scale, None, p_ref, None)
+    got = quest.quantize_int4(x.to(DEV), scale.to(DEV), None, torch.empty_like(p_ref, device=DEV))[2]
+    assert got.cpu().equal(p_ref)
+
+
+# ------------------------------------------------------------------ fused Hadamard + quantize ---------
+def check_hadamard_quantize(x: torch.Tensor, block: int) -> tuple[int, int, int]:
+    p_ref, s_ref, r_ref, xh_ref = O.hadamard_quantize_int4(x, block)
+    packed, scale, row_sum = quest.hadamard_quantize_int4(x.to(DEV), block)
+    xh = quest.hadamard_transform(x.to(DEV), block)
+    packed, scale, row_sum, xh = packed.cpu(), scale.cpu(), row_sum.cpu(), xh.cpu()
+    # the transform itself: at most one bf16 ulp apart, and only at rounding ties
+    ulp = O.bf16_ulp_distance(xh, xh_ref)
+    assert int(ulp.max()) <= 1
+    xh_mism = int((ulp != 0).sum())
+    # rows whose bf16 scale agrees must have codes that differ only by +-1 tie flips
+    same = (scale == s_ref).view(-1)
+    scale_flips = int((~same).sum())
+    assert int(O.bf16_ulp_distance(scale, s_ref).max()) <= 1
+    nflip, maxd = O.count_code_flips(packed[same], p_ref[same])
+    assert maxd <= 1
+    # row sums are consistent with the codes actually written
+    assert row_sum.equal(O.unpack_int4(packed).to(torch.int32).sum(-1, keepdim=True))
+    return xh_mism, nflip, scale_flips
+
+
+@pytest.mark.parametrize("block", [64, 128, 256])
+@pytest.mark.parametrize("kind,m,k", [("student", 128, 4096), ("laplace", 64, 8192), ("randn", 33, 14336),
+                                      ("outlier", 7, 2048), ("randn", 3, 28672), ("randn", 1, 256)])
+def test_hadamard_quantize_matches_oracle(block, kind, m, k):
+    x = make_activations(kind, m, k, seed=block + m)
+    xh_mism, nflip, scale_flips = check_hadamard_quantize(x, block)
+    n = m * k
+    # documented tolerance: tie flips only; expected rate <~ 1e-6 per element, asserted with headroom
+    assert xh_mism <= max(2, int(2e-5 * n)), (xh_mism, n)
+    assert nflip <= max(1, int(5e-6 * n)), (nflip, n)
+    assert scale_flips <= max(1, m // 1000)
+
+
+def test_hadamard_transform_weight_side_and_one_hot():
+    w = (0.02 * torch.randn(96, 1024, generator=torch.Generator().manual_seed(2))).to(torch.bfloat16)
+    ref = O.block_hadamard(w, 128, weight_side=True)
+    got = quest.hadamard_transform(w.to(DEV), 128, weight_side=True).cpu()
+    assert int(O.bf16_ulp_distance(got, ref).max()) <= 1 and (got != ref).float().mean() < 1e-4
+    e = torch.zeros(2, 256, dtype=torch.bfloat16)
+    e[0, 5] = 1
+    e[1, 128 + 77] = -2
+    got = quest.hadamard_transform(e.to(DEV), 128).cpu()
+    assert got.equal(O.block_hadamard(e, 128))
+
+
+# ------------------------------------------------------------------ int4 GEMM --------------------------
+GEMM_SHAPES = [
+    (160, 768, 224),      # the reference unit-test shape
+    (1, 128, 8), (16, 4096, 264), (127, 160, 100), (129, 32, 257), (128, 256, 256), (300, 1024, 520),
+    (256, 11008, 384),    # long K
+    (64, 28672, 136),     # longest K of the 70B-shaped layers
+    (1024, 512, 1024),    # many tiles per CTA: exercises the double-buffered accumulators
+]
+
+
+@pytest.mark.parametrize("m,k,n", GEMM_SHAPES)
+def test_matmul_int4_exact(m, k, n):
+    a = random_packed(m, k, seed=m + k)
+    b = random_packed(n, k, seed=n + k + 1)
+    c = quest.matmul_int4_int4t_int32(a.to(DEV), b.to(DEV))
+    assert c.dtype == torch.int32 and c.shape == (m, n)
+    assert c.cpu().equal(O.matmul_int4_int4t_int32(a, b))
+
+
+def test_matmul_int4_extreme_values():
+    """All codes -8: every accumulator equals 64 * K, the largest magnitude possible."""
+    m, k, n = 130, 28672, 72
+    a = torch.full((m, k // 2), 0x88, dtype=torch.uint8, device=DEV)
+    b = torch.full((n, k // 2), 0x88, dtype=torch.uint8, device=DEV)
+    c = quest.matmul_int4_int4t_int32(a, b)
+    assert int(c.min()) == 64 * k and int(c.max()) == 64 * k
+    b7 = torch.full((n, k // 2), 0x77, dtype=torch.uint8, device=DEV)
+    c = quest.matmul_int4_int4t_int32(a, b7)
+    assert int(c.min()) == -56 * k and int(c.max()) == -56 * k
+
+
+def test_matmul_int4_nibble_order():
+    """A one-hot code at column j of A and 1..K at B's columns picks out B[n, j]: checks nibble/K order."""
+    k, n = 256, 16
+    g = torch.Generator().manual_seed(5)
+    b_codes = torch.randint(-8, 8, (n, k), generator=g, dtype=torch.int8)
+    a_codes = torch.zeros(k, k, dtype=torch.int8)
+    a_codes[torch.arange(k), torch.arange(k)] = 1
+    c = quest.matmul_int4_int4t_int32(O.pack_int4(a_codes).to(DEV), O.pack_int4(b_codes).to(DEV))
+    assert c.cpu().equal(b_codes.t().to(torch.int32))
+
+
+def test_matmul_int4_output_reuse_and_out_argument():
+    a, b = random_packed(64, 512, 1), random_packed(96, 512, 2)
+    out = torch.full((64, 96), 12345, dtype=torch.int32, device=DEV)
+    ret = quest.matmul_int4_int4t_int32(a.to(DEV), b.to(DEV), out=out)
+    assert ret is out and out.cpu().equal(O.matmul_int4_int4t_int32(a, b))
+
+
+def test_matmul_full_size_checksums():
+    """Headline shape (M=2048, K=N=4096): row/column checksums against O(MK+NK) CPU arithmetic, and the
+    full result against cuBLAS int8 on the unpacked codes."""
+    m, k, n = 2048, 4096, 4096
+    a, b = random_packed(m, k, 11), random_packed(n, k, 12)
+    ad, bd = a.to(DEV), b.to(DEV)
+    c = quest.matmul_int4_int4t_int32(ad, bd)
+    ai, bi = O.unpack_int4(a).to(torch.int64), O.unpack_int4(b).to(torch.int64)
+    assert c.sum(dim=1).cpu().to(torch.int64).equal(ai @ bi.sum(dim=0))
+    assert c.sum(dim=0).cpu().to(torch.int64).equal(bi @ ai.sum(dim=0))
+    ref = torch._int_mm(quest.unpack_int4(ad), quest.unpack_int4(bd).t().contiguous())
+    assert c.equal(ref)
+
+
+# ------------------------------------------------------------------ epilogue ---------------------------
+def epilogue_inputs(m: int, n: int, seed: int):
+    g = torch.Generator().manual_seed(seed)
+    a_add = torch.randint(-8 * 64, 8 * 64, (m, 1), generator=g, dtype=torch.int32)
+    b_add = torch.randint(-8 * 64, 8 * 64, (n, 1), generator=g, dtype=torch.int32)
+    a_mul = (torch.rand(m, 1, generator=g) + 0.05).to(torch.bfloat16)
+    b_mul = (0.02 * torch.rand(n, 1, generator=g) + 0.001).to(torch.bfloat16)
+    return a_add, a_mul, b_add, b_mul
+
+
+@pytest.mark.parametrize("m,n", [(160, 224), (3, 8), (33, 100), (1, 7), (257, 4104)])
+def test_add_mul_vv_bit_exact(m, n):
+    a_add, a_mul, b_add, b_mul = epilogue_inputs(m, n, m + n)
+    c = torch.randint(-2 ** 20, 2 ** 20, (m, n), generator=torch.Generator().manual_seed(3), dtype=torch.int32)
+    ref = O.add_mul_vv(a_add, a_mul, b_add, b_mul, c)
+    got = quest.add_mul_vv(a_add.to(DEV), a_mul.to(DEV), b_add.to(DEV), b_mul.to(DEV), c.to(DEV))
+    assert got.cpu().equal(ref)
+
+
+@pytest.mark.parametrize("m,k,n", [(160, 768, 224), (16, 4096, 264), (129, 8192, 257), (300, 1024, 520), (1, 256, 4)])
+def test_fused_matmul_dequantize_bit_exact(m, k, n):
+    a, b = random_packed(m, k, 21), random_packed(n, k, 22)
+    a_add, a_mul, b_add, b_mul = epilogue_inputs(m, n, 23)
+    ref = O.fused_matmul_dequantize_int4_int4t_bf16(a, b, a_add, b_add, a_mul, b_mul)
+    got = quest.fused_matmul_dequantize_int4_int4t_bf16(a.to(DEV), b.to(DEV), a_add.to(DEV), b_add.to(DEV),
+                                                        a_mul.to(DEV), b_mul.to(DEV))
+    assert got.dtype == torch.bfloat16 and got.cpu().equal(ref)
+
+
+def test_fused_into_column_slice():
+    m, k, n, n_total = 96, 512, 128, 512
+    a, b = random_packed(m, k, 31), random_packed(n, k, 32)
+    a_add, a_mul, b_add, b_mul = epilogue_inputs(m, n, 33)
+    full = torch.zeros(m, n_total, dtype=torch.bfloat16, device=DEV)
+    quest.fused_matmul_dequantize_int4_int4t_bf16_into(a.to(DEV), b.to(DEV), a_add.to(DEV), b_add.to(DEV),
+                                                       a_mul.to(DEV), b_mul.to(DEV), full[:, 256:384])
+    ref = O.fused_matmul_dequantize_int4_int4t_bf16(a, b, a_add, b_add, a_mul, b_mul)
+    assert full[:, 256:384].cpu().equal(ref)
+    assert int(full[:, :256].abs().sum()) == 0 and int(full[:, 384:].abs().sum()) == 0
+
+
+# ------------------------------------------------------------------ layer / module ---------------------
+@pytest.mark.parametrize("case", GOLDEN_CASES)
+def test_linear_forward_matches_reference_golden(case):
+    gd = load_golden(case)
+    w = gd["weight"].to(DEV)
+    wp, ws, wa, meta = quest.preprocess_weight(w.clone(), use_hadamard=False)
+    assert meta is None
+    assert wp.cpu().equal(gd["w_int_packed"]) and ws.cpu().equal(gd["w_scale"]) and wa.cpu().equal(gd["w_add"])
+    y = quest.linear_forward(gd["activation"].to(DEV), wp, ws, wa, use_hadamard=False)
+    assert y.cpu().equal(gd["m"])
+    # debug route (int32 GEMM + add_mul_vv) gives the same bits
+    c = torch.empty(y.shape, dtype=torch.int32, device=DEV)
+    y2 = quest.linear_forward(gd["activation"].to(DEV), wp, ws, wa, use_hadamard=False, _c=c)
+    assert y2.equal(y) and c.cpu().equal(gd["c_ref"])
+
+
+def test_linear_forward_with_hadamard_config1():
+    """CPU-runnable config: x [512,2048] N(0,1) + 0.5 % x20 outliers, W [2048,2048] N(0,0.02), block 128."""
+    x = make_activations("outlier", 512, 2048, seed=0)
+    w = (0.02 * torch.randn(2048, 2048, generator=torch.Generator().manual_seed(0))).to(torch.bfloat16)
+    wp_ref, ws_ref, wa_ref, _ = O.preprocess_weight(w, use_hadamard=True)
+    wp, ws, wa, _ = quest.preprocess_weight(w.to(DEV), use_hadamard=True)
+    assert ws.cpu().equal(ws_ref)
+    nflip, maxd = O.count_code_flips(wp.cpu(), wp_ref)
+    assert maxd <= 1 and nflip <= 8
+    # with identical weights the layer output may differ only through activation tie flips
+    y = quest.linear_forward(x.to(DEV), wp_ref.to(DEV), ws_ref.to(DEV), wa_ref.to(DEV), use_hadamard=True).cpu()
+    y_ref = O.linear_forward(x, wp_ref, ws_ref, wa_ref, use_hadamard=True)
+    pa, sa, ra = quest.hadamard_quantize_int4(x.to(DEV))
+    pa_ref, sa_ref, ra_ref, _ = O.hadamard_quantize_int4(x)
+    if pa.cpu().equal(pa_ref) and sa.cpu().equal(sa_ref):
+        assert y.equal(y_ref)
+    else:
+        assert (y != y_ref).float().mean() < 0.02
+    rel = ((y.float() - y_ref.float()).norm() / y_ref.float().norm()).item()
+    assert rel < 1e-3
+    dense = x.float() @ w.float().t()
+    assert ((y.float() - dense).norm() / dense.norm()).item() < 0.25
+
+
+def test_linear4bit_module_and_workspaces():
+    torch.manual_seed(0)
+    lin = quest.Linear4bit(512, 384, bias=True, device=DEV, dtype=torch.bfloat16, use_hadamard=True)
+    assert lin.weight.is_meta and lin.w_int_packed.shape == (384, 256) and lin.w_meta_e is None
+    x = make_activations("student", 6 * 20, 512, seed=4).view(6, 20, 512).to(DEV)
+    y = lin(x)
+    assert y.shape == (6, 20, 384) and y.dtype == torch.bfloat16
+    flat = x.flatten(end_dim=-2)
+    ws = dict(_a_scale=torch.empty(120, 1, dtype=torch.bfloat16, device=DEV),
+              _a_int_packed=torch.empty(120, 256, dtype=torch.uint8, device=DEV),
+              _a_int_row_sum=torch.empty(120, 1, dtype=torch.int32, device=DEV))
+    out = torch.empty(120, 384, dtype=torch.bfloat16, device=DEV)
+    y2 = quest.linear_forward(flat, lin.w_int_packed, lin.w_scale, lin.w_add, out=out, use_hadamard=True, **ws)
+    assert y2 is out
+    assert (y2 + lin.bias).unflatten(0, (6, 20)).equal(y)
+    noop = quest.Linear4bit(512, 384, bias=False, device=DEV, dtype=torch.bfloat16, use_hadamard=True, use_noop=True)
+    assert int(noop(x).abs().sum()) == 0
+
+
+def test_cuda_graph_capture_and_replay():
+    """Mirrors the reference's graph test (gemm-quest/benchmarks/utils.py:765-784), for the whole layer."""
+    m, k, n = 160, 768, 224
+    a, b = random_packed(m, k, 41), random_packed(n, k, 42)
+    x = make_activations("randn", m, k, seed=43)
+    w = make_activations("randn", n, k, seed=44)
+    wp, ws, wa, _ = quest.preprocess_weight(w.to(DEV), use_hadamard=True)
+    gt = {
+        "a": torch.zeros(m, k // 2, dtype=torch.uint8, device=DEV), "b": torch.zeros(n, k // 2, dtype=torch.uint8, device=DEV),
+        "c": torch.zeros(m, n, dtype=torch.int32, device=DEV), "x": torch.zeros(m, k, dtype=torch.bfloat16, device=DEV),
+        "y": torch.zeros(m, n, dtype=torch.bfloat16, device=DEV),
+        "s": torch.empty(m, 1, dtype=torch.bfloat16, device=DEV), "p": torch.empty(m, k // 2, dtype=torch.uint8, device=DEV),
+        "r": torch.empty(m, 1, dtype=torch.int32, device=DEV),
+    }
+
+    def step():
+        quest.matmul_int4_int4t_int32(gt["a"], gt["b"], out=gt["c"])
+        quest.linear_forward(gt["x"], wp, ws, wa, out=gt["y"], _a_scale=gt["s"], _a_int_packed=gt["p"],
+                             _a_int_row_sum=gt["r"], use_hadamard=True)
+
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        for _ in range(3):
+            step()
+    torch.cuda.current_stream().wait_stream(s)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    gt["a"].copy_(a)
+    gt["b"].copy_(b)
+    gt["x"].copy_(x)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert gt["c"].cpu().equal(O.matmul_int4_int4t_int32(a, b))
+    assert gt["y"].equal(quest.linear_forward(x.to(DEV), wp, ws, wa, use_hadamard=True))

@@ -1,0 +1,358 @@
+"""Benchmark of the W4A4 QuEST linear layer on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+                    [--workload linear|gemm|hadamard_quantize] [--m M --k K --n N --block B]
+
+One "step" = one pass of the hot path over one batch of synthetic activations:
+    fused Hadamard+scale+quantise+pack kernel  ->  int4 GEMM with fused dequant epilogue  (-> all-gather, N>1)
+The default workload is the headline configuration M=2048, K=N=4096 (Llama-7B O-projection shape).
+With N GPUs every rank owns N=4096 output columns of a layer that is N*4096 columns wide (weak scaling),
+quantises the replicated activations itself and the column blocks are all-gathered.
+
+Prints ONE JSON line (rank 0).  `value` is whole-layer TOPS = 2*M*N_total*K / step time with inputs resident
+in HBM; `e2e` is the same metric through the public API with host buffers (pinned host -> device copy of the
+activations and device -> host copy of the result inside the timed region); `roofline` describes the dominant
+kernel (the GEMM) and `roofline_hadamard_quantize` the HBM-bound kernel; `cpu_baseline` times the CPU oracle
+port of the reference's torch path on this host's cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "W4A4 QuEST linear TOPS (M=2048,K=N=4096); Had+quant HBM GB/s; 1/2/4/8 GPU"
+L2_FLUSH_BYTES = 256 << 20  # > 126 MB L2
+
+
+# ----------------------------------------------------------------------------------------------------
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="linear", choices=["linear", "gemm", "hadamard_quantize"])
+    ap.add_argument("--m", type=int, default=2048)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--n", type=int, default=4096, help="output columns PER GPU")
+    ap.add_argument("--block", type=int, default=128)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def measured_peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def synthetic_inputs(m: int, k: int, n: int, seed: int = 0):
+    """Llama-7B-shaped sweep inputs: activations Student-t(nu=4) scaled to unit RMS, weights N(0, 0.02)."""
+    g = torch.Generator().manual_seed(seed)
+    z = torch.randn(m, k, generator=g)
+    chi = torch.randn(4, m, k, generator=g).square().sum(0)
+    x = z / (chi / 4).sqrt()
+    x = (x / x.square().mean().sqrt()).to(torch.bfloat16)
+    w = (0.02 * torch.randn(n, k, generator=g)).to(torch.bfloat16)
+    return x, w
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index, self.proc, self.path = gpu_index, None, None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.gpu_index), "-lms", "100"],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict | None:
+        if self.proc is None:
+            return None
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            f = [t.strip() for t in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if not sm:
+            return None
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(smax), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------------------------------
+def cpu_reference_run(args, steps: int, warmup: int) -> dict:
+    """The reference's torch CPU path for the same layer (oracle port: Hadamard as F.linear with the bf16
+    Hadamard matrix, baseline scale/quantise, exact matmul of the codes, baseline epilogue)."""
+    from oracle import quest_oracle as O
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    m, k, n = args.m, args.k, args.n
+    x, w = synthetic_inputs(m, k, n)
+    wp, ws, wa, _ = O.preprocess_weight(w, use_hadamard=True)
+    budget_s, times = 60.0, []
+    t_begin = time.perf_counter()
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        O.linear_forward(x, wp, ws, wa, use_hadamard=True, block=args.block, reference_op=True)
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+        if time.perf_counter() - t_begin > budget_s and len(times) >= 3:
+            break
+    t = sum(times) / len(times)
+    return {"seconds_per_step": t, "tops": 2.0 * m * n * k / t / 1e12, "cores": torch.get_num_threads(),
+            "steps_timed": len(times),
+            "sample": f"full layer M={m} K={k} N={n} block={args.block}, {len(times)} timed passes after {warmup} warm-ups"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    r = cpu_reference_run(args, steps=min(args.steps, 10), warmup=min(args.warmup, 2))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": r["tops"], "unit": "TOPS", "n_gpus": args.gpus,
+        "steps": r["steps_timed"], "warmup": min(args.warmup, 2), "ms_per_step": r["seconds_per_step"] * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int4 codes, fp32 exact matmul (CPU)",
+        "data": "synthetic",
+        "config": {"workload": f"W4A4 linear M={args.m} K={args.k} N={args.n} block={args.block} (CPU torch path)"},
+        "cpu_baseline": {"value": r["tops"], "unit": "TOPS", "cores": r["cores"], "kind": "port", "sample": r["sample"]},
+        "e2e": {"value": r["tops"], "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ----------------------------------------------------------------------------------------------------
+def run_b200(args):
+    import torch.distributed as dist
+    import quest_b200 as quest
+    from quest_b200.sharded import ShardedLinear4bit, shard_weight
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; quest_b200 has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = measured_peaks()
+
+    m, k, n_local = args.m, args.k, args.n
+    n_total = n_local * world
+    x_host, w_local = synthetic_inputs(m, k, n_local, seed=rank)  # each rank builds only its own weight shard
+    x_host, _ = synthetic_inputs(m, k, 8, seed=0)                 # activations are replicated: same seed everywhere
+    x = x_host.to(dev)
+    wp, ws, wa, _ = quest.preprocess_weight(w_local.to(dev), use_hadamard=True, block=args.block)
+    layer = ShardedLinear4bit((wp, ws, wa), n_total, rank, world, use_hadamard=True, block=args.block) if world > 1 else None
+    flush = torch.zeros(L2_FLUSH_BYTES // 4, dtype=torch.int32, device=dev)
+
+    a_scale = torch.empty(m, 1, dtype=torch.bfloat16, device=dev)
+    a_packed = torch.empty(m, k // 2, dtype=torch.uint8, device=dev)
+    a_rsum = torch.empty(m, 1, dtype=torch.int32, device=dev)
+    out = torch.empty(m, n_local, dtype=torch.bfloat16, device=dev)
+
+    def ev():
+        return torch.cuda.Event(enable_timing=True)
+
+    def step(timers=None):
+        """One pass.  Returns nothing; if `timers` is given, appends (t_f1, t_gemm, t_total) event triples."""
+        e0, e1, e2, e3 = ev(), ev(), ev(), ev()
+        if args.workload == "hadamard_quantize":
+            e0.record()
+            quest.hadamard_quantize_int4(x, args.block, a_packed, a_scale, a_rsum)
+            e1.record(); e2.record(); e3.record()
+        elif args.workload == "gemm":
+            e0.record(); e1.record()
+            quest.fused_matmul_dequantize_int4_int4t_bf16(a_packed, wp, a_rsum, wa, a_scale, ws, out)
+            e2.record(); e3.record()
+        elif world == 1:
+            e0.record()
+            quest.hadamard_quantize_int4(x, args.block, a_packed, a_scale, a_rsum)
+            e1.record()
+            quest.fused_matmul_dequantize_int4_int4t_bf16(a_packed, wp, a_rsum, wa, a_scale, ws, out)
+            e2.record(); e3.record()
+        else:
+            e0.record()
+            lws = layer.workspaces(m, k, dev, torch.bfloat16)
+            quest.hadamard_quantize_int4(x, args.block, lws["a_int_packed"], lws["a_scale"], lws["a_int_row_sum"])
+            e1.record()
+            quest.fused_matmul_dequantize_int4_int4t_bf16_into(lws["a_int_packed"], wp, lws["a_int_row_sum"], wa,
+                                                               lws["a_scale"], ws, lws["local"][:, :n_local])
+            e2.record()
+            dist.all_gather_into_tensor(lws["gathered"].view(-1), lws["local"].view(-1))
+            lws["out"].view(m, world, -1).copy_(lws["gathered"].permute(1, 0, 2))
+            e3.record()
+        if timers is not None:
+            timers.append((e0, e1, e2, e3))
+
+    if args.workload == "gemm":  # the GEMM-only workload needs quantised activations once
+        quest.hadamard_quantize_int4(x, args.block, a_packed, a_scale, a_rsum)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        flush.add_(1)
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    timers = []
+    wall0 = time.perf_counter()
+    for _ in range(args.steps):
+        flush.add_(1)  # evict the previous step's tensors from L2 (outside the event brackets)
+        step(timers)
+    barrier()
+    wall = time.perf_counter() - wall0
+    clocks = sampler.stop() if sampler else None
+
+    t_f1 = sum(e0.elapsed_time(e1) for e0, e1, _, _ in timers) / len(timers) * 1e-3
+    t_gemm = sum(e1.elapsed_time(e2) for _, e1, e2, _ in timers) / len(timers) * 1e-3
+    t_step = sum(e0.elapsed_time(e3) for e0, _, _, e3 in timers) / len(timers) * 1e-3
+    if world > 1:
+        tt = torch.tensor([t_step, t_f1, t_gemm], dtype=torch.float64, device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        t_step, t_f1, t_gemm = tt.tolist()
+
+    # ---- end to end through the public API, host buffers in and out ----
+    e2e = None
+    if not args.no_e2e and args.workload == "linear":
+        x_pin = x_host.pin_memory()
+        y_pin = torch.empty(m, n_total, dtype=torch.bfloat16).pin_memory()
+        x_dev = torch.empty_like(x)
+
+        def e2e_step():
+            x_dev.copy_(x_pin, non_blocking=True)
+            if world == 1:
+                y = quest.linear_forward(x_dev, wp, ws, wa, out=out, _a_scale=a_scale, _a_int_packed=a_packed,
+                                         _a_int_row_sum=a_rsum, use_hadamard=True, block=args.block)
+            else:
+                y = layer(x_dev)
+            y_pin.copy_(y, non_blocking=True)
+
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        ets = []
+        for _ in range(args.steps):
+            flush.add_(1)
+            s, e = ev(), ev()
+            s.record(); e2e_step(); e.record()
+            ets.append((s, e))
+        barrier()
+        t_e2e = sum(s.elapsed_time(e) for s, e in ets) / len(ets) * 1e-3
+        if world > 1:
+            tt = torch.tensor([t_e2e], dtype=torch.float64, device=dev)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            t_e2e = tt.item()
+        e2e = {"value": 2.0 * m * n_total * k / t_e2e / 1e12, "unit": "TOPS", "ms_per_step": t_e2e * 1e3,
+               "h2d_bytes_per_step": x_pin.numel() * 2, "d2h_bytes_per_step": y_pin.numel() * 2,
+               "api": "quest_b200.linear_forward" if world == 1 else "quest_b200.sharded.ShardedLinear4bit.forward"}
+
+    status = quest.device_status()
+    if status != 0:
+        raise RuntimeError(f"a kernel reported device status {status:#x}")
+
+    if rank == 0:
+        ops_total = 2.0 * m * n_total * k
+        ops_gemm = 2.0 * m * n_local * k
+        f1_bytes = 2.0 * m * k + m * k / 2 + 6.0 * m  # bf16 in + packed out + bf16 scale + int32 row sum
+        int8_peak = 2.0 * peaks["bf16_tflops"]        # tcgen05 kind::i8 runs at twice the bf16 rate
+        if args.workload == "hadamard_quantize":
+            value, unit, t_main = f1_bytes / t_f1 / 1e9, "GB/s", t_f1
+        elif args.workload == "gemm":
+            value, unit, t_main = ops_gemm / t_gemm / 1e12, "TOPS", t_gemm
+        else:
+            value, unit, t_main = ops_total / t_step / 1e12, "TOPS", t_step
+        launches_per_step = {"hadamard_quantize": 1, "gemm": 1}.get(args.workload, 2)
+        line = {
+            "metric": METRIC, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": t_main * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int4 operands, int8 tcgen05 MMA, int32 accumulate, bf16 out",
+            "data": "synthetic",
+            "config": {"workload": f"{args.workload}: W4A4 linear M={m} K={k} N={n_local} per GPU"
+                                   f" (N_total={n_total}), Hadamard block {args.block}",
+                       "l2": f"L2 flushed between timed steps by writing a {L2_FLUSH_BYTES >> 20} MiB buffer",
+                       "parallelism": f"N-sharded x{world} + all-gather" if world > 1 else "single GPU",
+                       "inputs": "activations Student-t(nu=4) unit RMS bf16; weights N(0,0.02) quantised to packed int4"},
+            "roofline": {"kernel": "gemm_i4_kernel (tcgen05 kind::i8, fused dequant epilogue)", "bound": "tensor",
+                         "achieved": ops_gemm / t_gemm / 1e12 if t_gemm > 0 else None, "peak": int8_peak,
+                         "unit": "TOPS", "frac": (ops_gemm / t_gemm / 1e12) / int8_peak if t_gemm > 0 else None,
+                         "peak_source": f"2 x bf16_tflops ({peaks['bf16_tflops']}) of {peaks['source']}",
+                         "traffic": None, "us_per_launch": t_gemm * 1e6},
+            "roofline_hadamard_quantize": {"kernel": "row_kernel<128> (fused Hadamard+scale+quantise+pack)", "bound": "hbm",
+                                           "achieved": f1_bytes / t_f1 / 1e9 if t_f1 > 0 else None,
+                                           "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                           "frac": (f1_bytes / t_f1 / 1e9) / peaks["hbm_gbs"] if t_f1 > 0 else None,
+                                           "peak_source": f"hbm_gbs of {peaks['source']}", "traffic": None,
+                                           "us_per_launch": t_f1 * 1e6, "algorithmic_bytes": f1_bytes},
+            "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
+            "wall_s_timed_region": wall,
+        }
+        if not args.no_cpu_baseline and world == 1 and args.workload == "linear":
+            r = cpu_reference_run(args, steps=5, warmup=1)
+            line["cpu_baseline"] = {"value": r["tops"], "unit": "TOPS", "cores": r["cores"], "kind": "port",
+                                    "sample": r["sample"], "ms_per_step": r["seconds_per_step"] * 1e3}
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

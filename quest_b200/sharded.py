@@ -1,0 +1,100 @@
+"""Column-sharded (N-sharded) W4A4 linear across the GPUs of one node.
+
+Each rank owns the weight rows [n0, n0 + N/g) (packed codes, per-row scales and offsets slice exactly,
+no re-quantisation), every rank quantises the replicated activations itself (cheap and deterministic,
+so all ranks hold identical codes), runs the fused GEMM for its N/g output columns and the column
+blocks are assembled with one all-gather.  Per element the arithmetic is the single-GPU arithmetic, so
+the assembled output is bit-identical to the 1-GPU result.  The reference has no multi-GPU inference
+path; this is the exchange step the sharding needs and nothing more.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+import quest_b200 as quest
+
+
+def shard_bounds(n_total: int, rank: int, world: int, align: int = 8) -> tuple[int, int]:
+    """[n0, n1) of the output columns owned by ``rank``.  Columns are dealt in multiples of ``align``
+    (16-byte bf16 stores) and the remainder goes to the last ranks one ``align`` block at a time."""
+    if n_total % align != 0:
+        raise ValueError(f"N={n_total} must be a multiple of {align} to be column-sharded")
+    blocks = n_total // align
+    base, extra = divmod(blocks, world)
+    counts = [base + (1 if r >= world - extra else 0) for r in range(world)]
+    n0 = sum(counts[:rank]) * align
+    return n0, n0 + counts[rank] * align
+
+
+def shard_weight(w_int_packed: torch.Tensor, w_scale: torch.Tensor, w_add: torch.Tensor, rank: int, world: int):
+    """Row slices of preprocess_weight's outputs for ``rank`` (contiguous copies)."""
+    n0, n1 = shard_bounds(w_int_packed.size(0), rank, world)
+    return (w_int_packed[n0:n1].contiguous(), w_scale[n0:n1].contiguous(), w_add[n0:n1].contiguous())
+
+
+class ShardedLinear4bit:
+    """One rank's part of a column-sharded W4A4 linear layer.
+
+    forward(x) returns the full [M, N_total] bf16 output on every rank.  Buffers are allocated once per
+    M (workspaces are reused across calls, so the steady state launches only kernels and one collective).
+    """
+
+    def __init__(self, w_shard: tuple[torch.Tensor, torch.Tensor, torch.Tensor], n_total: int, rank: int, world: int,
+                 group=None, use_hadamard: bool = True, block: int = 128):
+        self.w_int_packed, self.w_scale, self.w_add = w_shard
+        self.n_total, self.rank, self.world, self.group = n_total, rank, world, group
+        self.use_hadamard, self.block = use_hadamard, block
+        self.n0, self.n1 = shard_bounds(n_total, rank, world)
+        if self.w_int_packed.size(0) != self.n1 - self.n0:
+            raise ValueError("weight shard does not match this rank's column range")
+        self.widths = [shard_bounds(n_total, r, world)[1] - shard_bounds(n_total, r, world)[0] for r in range(world)]
+        self.width_max = max(self.widths)  # uneven splits gather equal-sized (padded) blocks
+        self._ws = {}
+
+    # -- compute for this rank's columns (CUDA kernels; overridden by the CPU tests of the host logic) --
+    def compute_shard(self, x: torch.Tensor, out_cols: torch.Tensor, ws: dict) -> None:
+        if self.use_hadamard:
+            quest.hadamard_quantize_int4(x, self.block, ws["a_int_packed"], ws["a_scale"], ws["a_int_row_sum"])
+        else:
+            quest.find_scale_int4(x, ws["a_scale"])
+            quest.quantize_int4(x, ws["a_scale"], None, ws["a_int_packed"], ws["a_int_row_sum"])
+        quest.fused_matmul_dequantize_int4_int4t_bf16_into(ws["a_int_packed"], self.w_int_packed, ws["a_int_row_sum"],
+                                                           self.w_add, ws["a_scale"], self.w_scale, out_cols)
+
+    def workspaces(self, m: int, k: int, device, dtype) -> dict:
+        key = (m, k, str(device))
+        if key not in self._ws:
+            self._ws[key] = dict(
+                a_scale=torch.empty(m, 1, dtype=dtype, device=device),
+                a_int_packed=torch.empty(m, k // 2, dtype=torch.uint8, device=device),
+                a_int_row_sum=torch.empty(m, 1, dtype=torch.int32, device=device),
+                local=torch.zeros(m, self.width_max, dtype=dtype, device=device),
+                gathered=torch.empty(self.world, m, self.width_max, dtype=dtype, device=device),
+                out=torch.empty(m, self.n_total, dtype=dtype, device=device),
+            )
+        return self._ws[key]
+
+    def forward(self, x: torch.Tensor, gather: bool = True) -> torch.Tensor:
+        m, k = x.shape
+        ws = self.workspaces(m, k, x.device, x.dtype)
+        out = ws["out"]
+        if self.world == 1:
+            self.compute_shard(x, out, ws)
+            return out
+        if not gather:
+            self.compute_shard(x, out[:, self.n0:self.n1], ws)
+            return out
+        # NCCL all-gather wants one contiguous, equal-sized block per rank: gather [g, M, width], then
+        # interleave the column blocks into the row-major [M, N_total] result.
+        self.compute_shard(x, ws["local"][:, :self.n1 - self.n0], ws)
+        dist.all_gather_into_tensor(ws["gathered"].view(-1), ws["local"].view(-1), group=self.group)
+        if self.width_max * self.world == self.n_total:
+            out.view(m, self.world, -1).copy_(ws["gathered"].permute(1, 0, 2))
+        else:
+            for r, w in enumerate(self.widths):
+                a, _ = shard_bounds(self.n_total, r, self.world)
+                out[:, a:a + w].copy_(ws["gathered"][r, :, :w])
+        return out
+
+    __call__ = forward

@@ -103,7 +103,7 @@ def test_quantize_generic_path_odd_shapes():
 
 def test_exact_integer_quotients_floor_correctly():
     """x / scale is an exact integer for ~1 % of real data; build rows where it is for EVERY element."""
-    scale = torch.tensor([[0.3359375], [1.0], [3.0517578125e-05], [24.0]], dtype=torch.bfloat16)
+    scale = torch.tensor([[0.3125], [1.0], [3.0517578125e-05], [24.0]], dtype=torch.bfloat16)  # <= 3-bit mantissas
     n = torch.arange(-10, 10, dtype=torch.float32).repeat(13)[:256]
     x = (n.view(1, -1) * scale.float()).to(torch.bfloat16)
     assert ((x.float() / scale.float()) == n).all()
@@ -119,9 +119,12 @@ def check_hadamard_quantize(x: torch.Tensor, block: int) -> tuple[int, int, int]
     packed, scale, row_sum = quest.hadamard_quantize_int4(x.to(DEV), block)
     xh = quest.hadamard_transform(x.to(DEV), block)
     packed, scale, row_sum, xh = packed.cpu(), scale.cpu(), row_sum.cpu(), xh.cpu()
-    # the transform itself: at most one bf16 ulp apart, and only at rounding ties
+    # the transform itself: one bf16 ulp apart at rounding ties; where a block cancels to (nearly) zero the
+    # fp32 summation error (<= 2^-20 of the block's absolute sum) can exceed an ulp of the tiny result
     ulp = O.bf16_ulp_distance(xh, xh_ref)
-    assert int(ulp.max()) <= 1
+    abs_sum = x.float().abs().view(x.size(0), -1, block).sum(-1, keepdim=True).expand(-1, -1, block).reshape(x.shape)
+    fp32_slack = abs_sum * O.hadamard_constant(block) * 2.0 ** -20
+    assert bool(((ulp <= 1) | ((xh.float() - xh_ref.float()).abs() <= fp32_slack)).all())
     xh_mism = int((ulp != 0).sum())
     # rows whose bf16 scale agrees must have codes that differ only by +-1 tie flips
     same = (scale == s_ref).view(-1)
@@ -141,9 +144,11 @@ def test_hadamard_quantize_matches_oracle(block, kind, m, k):
     x = make_activations(kind, m, k, seed=block + m)
     xh_mism, nflip, scale_flips = check_hadamard_quantize(x, block)
     n = m * k
-    # documented tolerance: tie flips only; expected rate <~ 1e-6 per element, asserted with headroom
-    assert xh_mism <= max(2, int(2e-5 * n)), (xh_mism, n)
-    assert nflip <= max(1, int(5e-6 * n)), (nflip, n)
+    # documented tolerance: tie flips only.  Transform outputs differ from the exact-sum oracle where the
+    # fp32 product sum * bf16(128^-0.5) is rounded twice (expected ~2^-15 of the elements for block 128,
+    # none for the power-of-two constants of blocks 64/256); codes flip by +-1 at <~ 1e-6 per element.
+    assert xh_mism <= 3 + int(1.5e-4 * n), (xh_mism, n)
+    assert nflip <= 1 + int(5e-6 * n), (nflip, n)
     assert scale_flips <= max(1, m // 1000)
 
 

@@ -4,6 +4,8 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdio.h>
+#include <stdlib.h>
 
 #include "../../include/quest_b200.h"
 
@@ -16,8 +18,14 @@ inline int cuda_status(cudaError_t e) { return e == cudaSuccess ? QB200_OK : QB2
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// Launch errors are sticky per thread; peek (do not clear another library's error) after each launch.
-inline int launch_status() { return cuda_status(cudaPeekAtLastError()); }
+// Status of the launch just made.  The error (if any) is returned to the caller as a status code and
+// cleared, so that it is not reported a second time by an unrelated later call.
+// With QB200_DEBUG set in the environment the CUDA error text goes to stderr.
+inline int launch_status() {
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess && getenv("QB200_DEBUG") != nullptr) fprintf(stderr, "quest_b200: %s\n", cudaGetErrorString(e));
+    return cuda_status(e);
+}
 
 // ---------------------------------------------------------------------------------------------
 // Device-side helpers

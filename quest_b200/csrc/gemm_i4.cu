@@ -158,8 +158,8 @@ constexpr int kNumThreads = kNumWarps * 32;
 template <int BN>
 struct Cfg {
     static constexpr int ROWS = BM + BN;                 // A rows then B rows, contiguous in shared memory
-    static constexpr int P_STAGES = 4;                   // packed ring  (TMA -> unpack)
-    static constexpr int U_STAGES = (BN == 256) ? 2 : 3; // int8 ring    (unpack -> MMA)
+    static constexpr int P_STAGES = (BN == 256) ? 3 : 4; // packed ring  (TMA -> unpack)
+    static constexpr int U_STAGES = 3;                   // int8 ring    (unpack -> MMA)
     static constexpr int P_BYTES = ROWS * PK_ROW;
     static constexpr int U_BYTES = ROWS * U8_ROW;
     static constexpr int TMEM_COLS = 2 * BN;             // two accumulator buffers (power of two >= 32)

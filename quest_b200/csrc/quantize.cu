@@ -28,6 +28,7 @@ struct RowParams {
     float had_scale;               // Hadamard normalisation constant
     int x_out_mode;                // 0 none, 1 transformed values, 2 dequantised values
     int quantize;                  // 0: stop after the scale (find_scale / transform only)
+    int dbg;                       // tuning aid: bit0 skip transform, bit1 skip quantise, bit2 skip square sum
 };
 
 constexpr int kUnit = 1024;        // elements per warp-unit
@@ -48,6 +49,21 @@ __device__ __forceinline__ int floor_quotient(float x, float inv_s) {
     const float y = x * inv_s;
     const float y2 = fmaf(fabsf(y), 1.220703125e-4f, y);
     return __float_as_int(__fadd_rd(y2, kFloorMagic)) - kFloorMagicBits;
+}
+
+// Same as floor_quotient but returns the raw bits of the magic-number sum: for |x/s| < 2^22 the low bits are
+// floor(x/s) in two's complement, so for a pre-clamped x the low nibble is the int4 code.
+__device__ __forceinline__ uint32_t floor_quotient_bits(float x, float inv_s) {
+    const float y = x * inv_s;
+    const float y2 = fmaf(fabsf(y), 1.220703125e-4f, y);
+    return __float_as_uint(__fadd_rd(y2, kFloorMagic));
+}
+
+// Element-wise clamp of a bf16 pair to [lo, hi] (both given as bf16 pairs).
+__device__ __forceinline__ uint32_t clamp_bf16x2(uint32_t v, uint32_t lo, uint32_t hi) {
+    uint32_t r;
+    asm("{\n\t.reg .b32 t;\n\tmax.bf16x2 t, %1, %2;\n\tmin.bf16x2 %0, t, %3;\n\t}" : "=r"(r) : "r"(v), "r"(lo), "r"(hi));
+    return r;
 }
 
 // (sat4(a) << 4 | sat4(b)) | (c << 8): saturating pack of two int32 to signed nibbles.
@@ -252,6 +268,356 @@ __global__ void __launch_bounds__(UNITS == 1 ? 256 : 512) row_kernel(const RowPa
             p.row_sum[row] = tot >> 4;  // exact: every term is a multiple of 16
         }
     }
+}
+
+// -------------------------------------------------------------------------------------------------
+// The hot path: fused Hadamard + scale + quantise + pack + row sum, tensor-core assisted.
+//
+// The shuffle-butterfly kernel above spends ~26 instructions per element and is issue-bound at well
+// under half of the HBM bandwidth.  Here the block transform is factored as H_block = H_a (x) H_16:
+// the 16-point factor over the low four index bits is a tiny bf16 MMA (mma.sync m16n8k16, A = sixteen
+// contiguous activations per row, B = +-bf16(block^-0.5) Sylvester signs, fp32 accumulate - the same
+// "x times Hadamard matrix" product the reference hands to cuBLAS), and the factor over the high index
+// bits is a butterfly over values a thread already holds.  Data path per warp and 1024 elements:
+//   cp.async 16 B/lane global -> warp-private shared memory (blocks padded to 272 B: conflict-free)
+//   ldmatrix x4  -> A fragments, 8 MMAs -> 32 fp32 values per thread (8 high-index rows x 4 columns)
+//   butterflies, round to bf16 pairs (kept in registers until the row's scale is known)
+//   quantise -> 2-byte pieces -> warp-private shared staging -> one coalesced 16-byte store per lane.
+// -------------------------------------------------------------------------------------------------
+constexpr int kBlkPitch = 272;              // 256-byte block of 128 bf16 + 16 bytes of padding
+constexpr int kStepIn = 8 * kBlkPitch;      // eight blocks per warp step
+constexpr int kOutPitch = 80;               // 64 packed bytes per block + 16 bytes of padding
+constexpr int kStepOut = 8 * kOutPitch;
+constexpr int kMaxDynSmem = 220 * 1024;  // leaves room for the static reduction arrays under the 227 KB limit
+constexpr int kStepBytes = 2 * kStepIn;  // two input buffers (the next row is prefetched); the packed codes are
+                                         // staged in the buffer that has just been consumed
+
+__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, bool valid) {
+    const int sz = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
+}
+
+// Thread-block shape: G row groups x W warps.  The W warps of a group share one row (UNITS 1024-element
+// units per warp); the block walks over batches of G rows.  Everything that is per row rather than per
+// element (summing the partial sums, sqrt, rounding the scale, its reciprocal, the clamp bounds, the final
+// row sum) is done once per batch by warp 0, one row per lane, so it costs a few instructions per row
+// instead of a hundred per thread.
+struct HqRowConst {
+    float inv_s;
+    uint32_t lo2, hi2;  // clamp bounds -8s and ~7.5s as bf16 pairs
+    uint32_t pad;
+};
+
+template <int HB, int UNITS>
+__global__ void __launch_bounds__(256, UNITS == 1 ? 4 : (UNITS == 2 ? 3 : 2))
+hadamard_quant_mma_kernel(const RowParams p, const int W, const int G) {
+    extern __shared__ __align__(16) uint8_t hq_smem[];
+    __shared__ float part_ssq[8];
+    __shared__ int part_rs[8];
+    __shared__ HqRowConst row_const[8];
+
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int grp = warp / W;      // row group of this warp
+    const int wig = warp - grp * W;  // warp index within the group
+    const int g = lane >> 2, tig = lane & 3;
+    const int K = p.K, M = p.M;
+    const uint32_t smem_w = (uint32_t)__cvta_generic_to_shared(hq_smem) + warp * (UNITS * kStepBytes);
+    const int num_batches = (M + G - 1) / G;
+
+    // Copies of this warp's units of one row into input buffer `buf` (16 bytes per lane and instruction).
+    auto issue_row = [&](int row, int buf) {
+        if (row < M) {
+            const __nv_bfloat16* xr = p.x + (size_t)row * K;
+#pragma unroll
+            for (int u = 0; u < UNITS; ++u) {
+                const int unit = u * W + wig;
+                const uint32_t in_base = smem_w + u * kStepBytes + buf * kStepIn;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int c = j * 32 + lane;  // 16-byte chunk within the unit
+                    const int e = unit * kUnit + c * 8;
+                    const bool valid = e < K;
+                    cp_async16_zfill(in_base + (c >> 4) * kBlkPitch + (c & 15) * 16,
+                                     valid ? (const void*)(xr + e) : (const void*)xr, valid);
+                }
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    int batch = blockIdx.x;
+    if (batch < num_batches) issue_row(batch * G + grp, 0);
+
+    // ---- B fragments: h * H16[k][o], MMA column n of tile nu is output o = 4*(n>>1) + 2*nu + (n&1) ----
+    uint32_t bfrag[2][2];
+    {
+        const uint32_t hb = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(p.had_scale));
+#pragma unroll
+        for (int nu = 0; nu < 2; ++nu) {
+            const int o = 4 * (g >> 1) + 2 * nu + (g & 1);
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int k0 = 2 * tig + 8 * half;
+                const uint32_t lo = hb | ((__popc(k0 & o) & 1) ? 0x8000u : 0u);
+                const uint32_t hi = hb | ((__popc((k0 + 1) & o) & 1) ? 0x8000u : 0u);
+                bfrag[nu][half] = lo | (hi << 16);
+            }
+        }
+    }
+
+    int prev_batch = -1;
+    for (int it = 0; batch < num_batches; batch += gridDim.x, ++it) {
+        const int buf = it & 1;
+        const int row = batch * G + grp;
+        const int next = batch + gridDim.x;
+        if (next < num_batches) {
+            issue_row(next * G + grp, buf ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncwarp();
+
+        uint32_t v[UNITS][16];  // v[u][2a + nu]: elements 16a + 4tig + 2nu (+1) of block g of the unit
+        float ssq = 0.f;
+#pragma unroll
+        for (int u = 0; u < UNITS; ++u) {
+            const uint32_t in_base = smem_w + u * kStepBytes + buf * kStepIn;
+            float f[8][4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                uint32_t a[4];
+                ldmatrix_x4(in_base + (lane & 7) * kBlkPitch + (2 * t + ((lane >> 3) & 1)) * 32 + (lane >> 4) * 16, a);
+#pragma unroll
+                for (int nu = 0; nu < 2; ++nu) {
+                    float d[4];
+                    if (p.dbg & 1) { d[0] = __uint_as_float(a[0]); d[1] = __uint_as_float(a[1]); d[2] = __uint_as_float(a[2]); d[3] = __uint_as_float(a[3]); }
+                    else mma_bf16_16816(d, a, bfrag[nu][0], bfrag[nu][1]);
+                    f[2 * t][2 * nu] = d[0];
+                    f[2 * t][2 * nu + 1] = d[1];
+                    f[2 * t + 1][2 * nu] = d[2];
+                    f[2 * t + 1][2 * nu + 1] = d[3];
+                }
+            }
+            // remaining index bits 4.. of the block: butterflies over the row index a (in registers)
+            if (!(p.dbg & 1))
+#pragma unroll
+            for (int s = 1; s < 8 && s < HB / 16; s <<= 1) {
+#pragma unroll
+                for (int a = 0; a < 8; ++a) {
+                    if ((a & s) == 0) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float x0 = f[a][j], x1 = f[a + s][j];
+                            f[a][j] = x0 + x1;
+                            f[a + s][j] = x0 - x1;
+                        }
+                    }
+                }
+            }
+            if (HB == 256) {  // index bit 7 pairs neighbouring 128-element halves: lanes g and g ^ 1
+                const float sgn = (g & 1) ? -1.f : 1.f;
+#pragma unroll
+                for (int a = 0; a < 8; ++a)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float pv = __shfl_xor_sync(0xffffffffu, f[a][j], 4);
+                        f[a][j] = fmaf(f[a][j], sgn, pv);
+                    }
+            }
+#pragma unroll
+            for (int a = 0; a < 8; ++a) {
+                v[u][2 * a] = pack_bf16x2(f[a][0], f[a][1]);
+                v[u][2 * a + 1] = pack_bf16x2(f[a][2], f[a][3]);
+            }
+            if (!(p.dbg & 4))
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float x0 = bf16lo_to_f32(v[u][i]), x1 = bf16hi_to_f32(v[u][i]);
+                ssq = fmaf(x0, x0, ssq);
+                ssq = fmaf(x1, x1, ssq);
+            }
+        }
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, m);
+        if (lane == 0) part_ssq[warp] = ssq;
+        __syncthreads();  // B1: partial sums of this batch (and row-sum partials of the previous one) are in place
+
+        if (warp == 0 && lane < G) {
+            const int r = batch * G + lane;
+            if (r < M) {
+                double tot = 0.0;
+                for (int i = 0; i < W; ++i) tot += (double)part_ssq[lane * W + i];
+                const __nv_bfloat16 sb = __float2bfloat16_rn(quest_scale_from_mean_square((float)(tot / (double)K)));
+                p.scale_out[r] = sb;
+                const float s_f = bf16_to_f32(sb);
+                const uint32_t lo1 = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(-8.f * s_f));
+                const uint32_t hi1 = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(7.5f * s_f));
+                HqRowConst rc;
+                rc.inv_s = __frcp_rn(s_f);
+                rc.lo2 = lo1 | (lo1 << 16);
+                rc.hi2 = hi1 | (hi1 << 16);
+                rc.pad = 0;
+                row_const[lane] = rc;
+            }
+            if (prev_batch >= 0 && p.row_sum != nullptr) {
+                const int pr = prev_batch * G + lane;
+                if (pr < M) {
+                    int t2 = 0;
+                    for (int i = 0; i < W; ++i) t2 += part_rs[lane * W + i];
+                    p.row_sum[pr] = t2 >> 4;  // exact: every term is a multiple of 16
+                }
+            }
+        }
+        __syncthreads();  // B2: the row constants are published
+
+        // ---- quantise, stage, store ----
+        // Saturation is done on the bf16 pairs before the divide: x is clamped to [-8s, ~7.5s], both bounds
+        // exact or safely inside [7s, 8s), so floor(x/s) lands in [-8, 7] without integer min/max, and the
+        // code is simply the low nibble of the magic-number sum.
+        const HqRowConst rc = row_const[grp];
+        const float inv_s = rc.inv_s;
+        const uint32_t lo2 = rc.lo2, hi2 = rc.hi2;
+        const bool vec_store = (K & 31) == 0;
+        int rs16 = 0;
+        if (p.dbg & 2) { rs16 = v[0][0] ^ v[UNITS - 1][15]; } else
+#pragma unroll
+        for (int u = 0; u < UNITS; ++u) {
+            const int unit = u * W + wig;
+            const uint32_t out_base = smem_w + u * kStepBytes + buf * kStepIn;  // input already consumed
+#pragma unroll
+            for (int pr = 0; pr < 4; ++pr) {  // rows a = 2pr and 2pr + 1: eight codes -> one 32-bit word
+                uint32_t ub[8];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint32_t c = clamp_bf16x2(v[u][4 * pr + i], lo2, hi2);
+                    ub[2 * i] = floor_quotient_bits(bf16lo_to_f32(c), inv_s);
+                    ub[2 * i + 1] = floor_quotient_bits(bf16hi_to_f32(c), inv_s);
+                }
+                // ub[0..3] = row 2pr elements 0..3, ub[4..7] = row 2pr+1 elements 0..3; code = low nibble
+                const uint32_t ev = __byte_perm(__byte_perm(ub[0], ub[2], 0x0040), __byte_perm(ub[4], ub[6], 0x0040), 0x5410);
+                const uint32_t od = __byte_perm(__byte_perm(ub[1], ub[3], 0x0040), __byte_perm(ub[5], ub[7], 0x0040), 0x5410);
+                const uint32_t word = (ev & 0x0F0F0F0Fu) | ((od << 4) & 0xF0F0F0F0u);
+                asm volatile("st.shared.b32 [%0], %1;" ::"r"(out_base + g * kOutPitch + pr * 16 + tig * 4), "r"(word) : "memory");
+            }
+            __syncwarp();
+            uint4 t4;  // lane reads rows (2c, 2c+1) of block lane>>2, c = lane&3: one word per source thread tig
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(t4.x), "=r"(t4.y), "=r"(t4.z), "=r"(t4.w) : "r"(out_base + (lane >> 2) * kOutPitch + (lane & 3) * 16));
+            __syncwarp();  // the staging area is rewritten for the next row
+            uint4 w;   // low halves are row 2c (bytes 2tig, 2tig+1), high halves row 2c+1
+            w.x = __byte_perm(t4.x, t4.y, 0x5410);
+            w.y = __byte_perm(t4.z, t4.w, 0x5410);
+            w.z = __byte_perm(t4.x, t4.y, 0x7632);
+            w.w = __byte_perm(t4.z, t4.w, 0x7632);
+            rs16 = nibble_sum16(w.x, rs16);
+            rs16 = nibble_sum16(w.y, rs16);
+            rs16 = nibble_sum16(w.z, rs16);
+            rs16 = nibble_sum16(w.w, rs16);
+            const int e0 = unit * kUnit + lane * 32;
+            if (row < M) {
+                uint8_t* dst = p.q_packed + (size_t)row * (K >> 1) + (e0 >> 1);
+                if (vec_store) {
+                    if (e0 < K) *reinterpret_cast<uint4*>(dst) = w;
+                } else {
+                    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        if (e0 + 8 * j < K) *reinterpret_cast<uint32_t*>(dst + 4 * j) = ww[j];
+                }
+            }
+        }
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) rs16 += __shfl_xor_sync(0xffffffffu, rs16, m);
+        if (lane == 0) part_rs[warp] = rs16;
+        prev_batch = batch;
+    }
+    // row sums of the last batch
+    __syncthreads();
+    if (warp == 0 && lane < G && prev_batch >= 0 && p.row_sum != nullptr) {
+        const int pr = prev_batch * G + lane;
+        if (pr < M) {
+            int t2 = 0;
+            for (int i = 0; i < W; ++i) t2 += part_rs[lane * W + i];
+            p.row_sum[pr] = t2 >> 4;
+        }
+    }
+}
+
+template <int HB, bool EXTRAS>
+static int launch_row(const RowParams& p, cudaStream_t stream);
+
+template <int HB>
+static int launch_hq_mma(const RowParams& p, cudaStream_t stream) {
+    const int units = (p.K + kUnit - 1) / kUnit;
+    // units per warp, warps per row, rows per block (at most 16 warps per block)
+    int per = units >= 2 ? 2 : 1;
+    if (const char* e = getenv("QB200_HQ_UNITS")) per = atoi(e);  // tuning aid
+    if (per > units) per = units;
+    if (per != 1 && per != 2 && per != 4) per = 2;
+    int W = (units + per - 1) / per;
+    if (W > 8 && per < 4) { per = 4; W = (units + per - 1) / per; }
+    if (W > 8) return launch_row<HB, false>(p, stream);  // very long rows: shuffle-butterfly kernel
+    int G = 8 / W;
+    if (const char* e = getenv("QB200_HQ_G")) G = atoi(e);  // tuning aid
+    if (G * W > 8) G = 8 / W;
+    if (G < 1) G = 1;
+    if (G > p.M) G = p.M;
+    const int warps = W * G;
+    const size_t smem = (size_t)warps * per * kStepBytes;
+    if (smem > kMaxDynSmem) return launch_row<HB, false>(p, stream);
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) != cudaSuccess) return QB200_ERR_CUDA;
+    {
+        static int cached[64] = {0};
+        if (dev >= 0 && dev < 64 && cached[dev] > 0) sms = cached[dev];
+        else if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0) {
+            if (dev >= 0 && dev < 64) cached[dev] = sms;
+        } else sms = 148;
+    }
+    // Persistent grid: as many blocks as fit on the device at once (bounded by the number of row batches).
+    // The caches are per kernel instantiation (index `which`) and per device.
+    static bool attr_done[3][64] = {{false}};
+    static int occ_cache[3][64][9] = {{{0}}};
+    auto launch = [&](auto kernel, int which) -> int {
+        const bool dev_ok = dev >= 0 && dev < 64;
+        if (!(dev_ok && attr_done[which][dev])) {
+            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem) != cudaSuccess) {
+                cudaGetLastError();  // reported through the return value; do not leave it pending
+                return QB200_ERR_CUDA;
+            }
+            if (dev_ok) attr_done[which][dev] = true;
+        }
+        int occ = dev_ok ? occ_cache[which][dev][warps] : 0;
+        if (occ <= 0) {
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, 32 * warps, smem) != cudaSuccess || occ <= 0) {
+                cudaGetLastError();
+                occ = 1;
+            }
+            if (dev_ok) occ_cache[which][dev][warps] = occ;
+        }
+        const long long batches = ((long long)p.M + G - 1) / G;
+        long long grid = (long long)sms * occ;
+        if (grid > batches) grid = batches;
+        kernel<<<(unsigned)grid, 32 * warps, smem, stream>>>(p, W, G);
+        return launch_status();
+    };
+    if (per == 1) return launch(hadamard_quant_mma_kernel<HB, 1>, 0);
+    if (per == 2) return launch(hadamard_quant_mma_kernel<HB, 2>, 1);
+    return launch(hadamard_quant_mma_kernel<HB, 4>, 2);
 }
 
 // Any K, any alignment, no Hadamard: one block per row, scalar accesses.  Only used for shapes the
@@ -478,7 +844,13 @@ extern "C" int hadamard_quantize_int4_cuda_bf16(void* x_int_packed_ptr, void* sc
     p.M = batch_size;
     p.quantize = 1;
     p.had_scale = __bfloat162float(__float2bfloat16_rn((float)(1.0 / sqrt((double)block))));
-    return run_rows(p, block, false, stream);
+    if (const char* e = getenv("QB200_HQ_DBG")) p.dbg = atoi(e);
+    if (!vector_path_ok(p)) return QB200_ERR_UNSUPPORTED;
+    switch (block) {
+        case 64: return launch_hq_mma<64>(p, stream);
+        case 128: return launch_hq_mma<128>(p, stream);
+        default: return launch_hq_mma<256>(p, stream);
+    }
 }
 
 extern "C" int hadamard_transform_cuda_bf16(void* out_ptr, const void* x_ptr, int group_size, int batch_size,

@@ -140,6 +140,7 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
     asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
+
 // ---------------------------------------------------------------------------------------------
 // Tile configuration
 // ---------------------------------------------------------------------------------------------
@@ -162,7 +163,7 @@ struct Cfg {
     static constexpr int U_STAGES = 3;                   // int8 ring    (unpack -> MMA)
     static constexpr int P_BYTES = ROWS * PK_ROW;
     static constexpr int U_BYTES = ROWS * U8_ROW;
-    static constexpr int TMEM_COLS = 2 * BN;             // two accumulator buffers (power of two >= 32)
+    static constexpr int TMEM_COLS = (2 * BN > 256) ? 512 : 256;  // two accumulator buffers, power of two
     static constexpr int NUM_BARS = 2 * P_STAGES + 2 * U_STAGES + 4 + 1;
     static constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + U_STAGES * U_BYTES + P_STAGES * P_BYTES + NUM_BARS * 8 + 16;
     // instruction descriptor: D=s32, A=B=s8, both K-major, N and M of the MMA
@@ -185,6 +186,71 @@ struct EpilogueParams {
     const __nv_bfloat16* b_mul;  // [N]
     int vec_ok;             // 16-byte stores are aligned for every (row, 8-column group)
 };
+
+
+// Converts and stores 32 consecutive accumulators of one output row (columns col0 .. col0+31, clipped to N).
+// The accumulators carry the factor 256 of the unpack; FUSED applies the exact dequantising expression
+//   D = bf16( float(2*acc + a_add[m] + b_add[n]) * (0.5f * a_mul[m] * b_mul[n]) ),
+// otherwise the int32 accumulators are written.
+template <bool FUSED>
+__device__ __forceinline__ void epilogue_store_chunk(const uint32_t (&r)[32], const EpilogueParams& ep, int row, int col0,
+                                                     int N, int a_add, float half_a_mul) {
+    if (FUSED) {
+        __nv_bfloat16* out = static_cast<__nv_bfloat16*>(ep.out) + (size_t)row * ep.ld + col0;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            const int col = col0 + 8 * g;
+            if (ep.vec_ok && col + 8 <= N) {
+                const int4 b0 = __ldg(reinterpret_cast<const int4*>(ep.b_add + col));
+                const int4 b1 = __ldg(reinterpret_cast<const int4*>(ep.b_add + col + 4));
+                const uint4 bm = __ldg(reinterpret_cast<const uint4*>(ep.b_mul + col));
+                const int ba[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+                const uint32_t bmw[4] = {bm.x, bm.y, bm.z, bm.w};
+                uint32_t o[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int acc0 = (int)r[8 * g + 2 * i] >> 8, acc1 = (int)r[8 * g + 2 * i + 1] >> 8;
+                    const float v0 = (float)(acc0 * 2 + a_add + ba[2 * i]) * (half_a_mul * bf16lo_to_f32(bmw[i]));
+                    const float v1 = (float)(acc1 * 2 + a_add + ba[2 * i + 1]) * (half_a_mul * bf16hi_to_f32(bmw[i]));
+                    o[i] = pack_bf16x2(v0, v1);
+                }
+                *reinterpret_cast<uint4*>(out + 8 * g) = make_uint4(o[0], o[1], o[2], o[3]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    if (col + i < N) {
+                        const int acc0 = (int)r[8 * g + i] >> 8;
+                        const float v0 = (float)(acc0 * 2 + a_add + ep.b_add[col + i]) *
+                                         (half_a_mul * bf16_to_f32(ep.b_mul[col + i]));
+                        out[8 * g + i] = __float2bfloat16_rn(v0);
+                    }
+                }
+            }
+        }
+    } else {
+        int32_t* out = static_cast<int32_t*>(ep.out) + (size_t)row * ep.ld + col0;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+            const int col = col0 + 4 * g;
+            if (ep.vec_ok && col + 4 <= N) {
+                *reinterpret_cast<int4*>(out + 4 * g) =
+                    make_int4((int)r[4 * g] >> 8, (int)r[4 * g + 1] >> 8, (int)r[4 * g + 2] >> 8, (int)r[4 * g + 3] >> 8);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    if (col + i < N) out[4 * g + i] = (int)r[4 * g + i] >> 8;
+            }
+        }
+    }
+}
+
+// The 16 bytes (32 codes) pk unpacked to the two 16-byte int8 chunks of the "times sixteen" form.
+__device__ __forceinline__ void unpack_x16(const uint4& pk, uint4& lo, uint4& hi) {
+    lo.x = (pk.x << 4) & 0xF0F0F0F0u; hi.x = pk.x & 0xF0F0F0F0u;
+    lo.y = (pk.y << 4) & 0xF0F0F0F0u; hi.y = pk.y & 0xF0F0F0F0u;
+    lo.z = (pk.z << 4) & 0xF0F0F0F0u; hi.z = pk.z & 0xF0F0F0F0u;
+    lo.w = (pk.w << 4) & 0xF0F0F0F0u; hi.w = pk.w & 0xF0F0F0F0u;
+}
 
 // ---------------------------------------------------------------------------------------------
 // The kernel
@@ -327,54 +393,7 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 tmem_ld32(t_row + c0, r);
                 tmem_ld_wait();
                 if (!row_ok) continue;
-                const int col0 = n0 + c0;
-                if (FUSED) {
-                    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(ep.out) + (size_t)row * ep.ld + col0;
-#pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        const int col = col0 + 8 * g;
-                        if (ep.vec_ok && col + 8 <= N) {
-                            const int4 b0 = __ldg(reinterpret_cast<const int4*>(ep.b_add + col));
-                            const int4 b1 = __ldg(reinterpret_cast<const int4*>(ep.b_add + col + 4));
-                            const uint4 bm = __ldg(reinterpret_cast<const uint4*>(ep.b_mul + col));
-                            const int ba[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-                            const uint32_t bmw[4] = {bm.x, bm.y, bm.z, bm.w};
-                            uint32_t o[4];
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const int acc0 = (int)r[8 * g + 2 * i] >> 8, acc1 = (int)r[8 * g + 2 * i + 1] >> 8;
-                                const float v0 = (float)(acc0 * 2 + a_add + ba[2 * i]) * (half_a_mul * bf16lo_to_f32(bmw[i]));
-                                const float v1 = (float)(acc1 * 2 + a_add + ba[2 * i + 1]) * (half_a_mul * bf16hi_to_f32(bmw[i]));
-                                o[i] = pack_bf16x2(v0, v1);
-                            }
-                            *reinterpret_cast<uint4*>(out + 8 * g) = make_uint4(o[0], o[1], o[2], o[3]);
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                if (col + i < N) {
-                                    const int acc0 = (int)r[8 * g + i] >> 8;
-                                    const float v0 = (float)(acc0 * 2 + a_add + ep.b_add[col + i]) *
-                                                     (half_a_mul * bf16_to_f32(ep.b_mul[col + i]));
-                                    out[8 * g + i] = __float2bfloat16_rn(v0);
-                                }
-                            }
-                        }
-                    }
-                } else {
-                    int32_t* out = static_cast<int32_t*>(ep.out) + (size_t)row * ep.ld + col0;
-#pragma unroll
-                    for (int g = 0; g < 8; ++g) {
-                        const int col = col0 + 4 * g;
-                        if (ep.vec_ok && col + 4 <= N) {
-                            *reinterpret_cast<int4*>(out + 4 * g) =
-                                make_int4((int)r[4 * g] >> 8, (int)r[4 * g + 1] >> 8, (int)r[4 * g + 2] >> 8, (int)r[4 * g + 3] >> 8);
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 4; ++i)
-                                if (col + i < N) out[4 * g + i] = (int)r[4 * g + i] >> 8;
-                        }
-                    }
-                }
+                epilogue_store_chunk<FUSED>(r, ep, row, n0 + c0, N, a_add, half_a_mul);
             }
             // This warp has finished reading the accumulator buffer.
             tc_fence_before();
@@ -433,6 +452,7 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         tmem_dealloc(tmem_acc, C::TMEM_COLS);
     }
 }
+
 
 // ---------------------------------------------------------------------------------------------
 // Host side
@@ -503,6 +523,7 @@ static int launch_gemm(const EpilogueParams& ep, const void* a, const void* b, i
     kernel<<<grid, kNumThreads, C::SMEM_BYTES, stream>>>(ma, mb, ep, M, N, K);
     return launch_status();
 }
+
 
 static int pick_bn(int M, int N, int sms) {
     // Prefer the 128x256 tile (more reuse per byte of shared-memory traffic) unless the narrower tile

@@ -28,7 +28,6 @@ struct RowParams {
     float had_scale;               // Hadamard normalisation constant
     int x_out_mode;                // 0 none, 1 transformed values, 2 dequantised values
     int quantize;                  // 0: stop after the scale (find_scale / transform only)
-    int dbg;                       // tuning aid: bit0 skip transform, bit1 skip quantise, bit2 skip square sum
 };
 
 constexpr int kUnit = 1024;        // elements per warp-unit
@@ -287,7 +286,6 @@ __global__ void __launch_bounds__(UNITS == 1 ? 256 : 512) row_kernel(const RowPa
 constexpr int kBlkPitch = 272;              // 256-byte block of 128 bf16 + 16 bytes of padding
 constexpr int kStepIn = 8 * kBlkPitch;      // eight blocks per warp step
 constexpr int kOutPitch = 80;               // 64 packed bytes per block + 16 bytes of padding
-constexpr int kStepOut = 8 * kOutPitch;
 constexpr int kMaxDynSmem = 220 * 1024;  // leaves room for the static reduction arrays under the 227 KB limit
 constexpr int kStepBytes = 2 * kStepIn;  // two input buffers (the next row is prefetched); the packed codes are
                                          // staged in the buffer that has just been consumed
@@ -404,8 +402,7 @@ hadamard_quant_mma_kernel(const RowParams p, const int W, const int G) {
 #pragma unroll
                 for (int nu = 0; nu < 2; ++nu) {
                     float d[4];
-                    if (p.dbg & 1) { d[0] = __uint_as_float(a[0]); d[1] = __uint_as_float(a[1]); d[2] = __uint_as_float(a[2]); d[3] = __uint_as_float(a[3]); }
-                    else mma_bf16_16816(d, a, bfrag[nu][0], bfrag[nu][1]);
+                    mma_bf16_16816(d, a, bfrag[nu][0], bfrag[nu][1]);
                     f[2 * t][2 * nu] = d[0];
                     f[2 * t][2 * nu + 1] = d[1];
                     f[2 * t + 1][2 * nu] = d[2];
@@ -413,7 +410,6 @@ hadamard_quant_mma_kernel(const RowParams p, const int W, const int G) {
                 }
             }
             // remaining index bits 4.. of the block: butterflies over the row index a (in registers)
-            if (!(p.dbg & 1))
 #pragma unroll
             for (int s = 1; s < 8 && s < HB / 16; s <<= 1) {
 #pragma unroll
@@ -443,7 +439,6 @@ hadamard_quant_mma_kernel(const RowParams p, const int W, const int G) {
                 v[u][2 * a] = pack_bf16x2(f[a][0], f[a][1]);
                 v[u][2 * a + 1] = pack_bf16x2(f[a][2], f[a][3]);
             }
-            if (!(p.dbg & 4))
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
                 const float x0 = bf16lo_to_f32(v[u][i]), x1 = bf16hi_to_f32(v[u][i]);
@@ -493,7 +488,6 @@ hadamard_quant_mma_kernel(const RowParams p, const int W, const int G) {
         const uint32_t lo2 = rc.lo2, hi2 = rc.hi2;
         const bool vec_store = (K & 31) == 0;
         int rs16 = 0;
-        if (p.dbg & 2) { rs16 = v[0][0] ^ v[UNITS - 1][15]; } else
 #pragma unroll
         for (int u = 0; u < UNITS; ++u) {
             const int unit = u * W + wig;
@@ -565,14 +559,12 @@ static int launch_hq_mma(const RowParams& p, cudaStream_t stream) {
     const int units = (p.K + kUnit - 1) / kUnit;
     // units per warp, warps per row, rows per block (at most 16 warps per block)
     int per = units >= 2 ? 2 : 1;
-    if (const char* e = getenv("QB200_HQ_UNITS")) per = atoi(e);  // tuning aid
     if (per > units) per = units;
     if (per != 1 && per != 2 && per != 4) per = 2;
     int W = (units + per - 1) / per;
     if (W > 8 && per < 4) { per = 4; W = (units + per - 1) / per; }
     if (W > 8) return launch_row<HB, false>(p, stream);  // very long rows: shuffle-butterfly kernel
     int G = 8 / W;
-    if (const char* e = getenv("QB200_HQ_G")) G = atoi(e);  // tuning aid
     if (G * W > 8) G = 8 / W;
     if (G < 1) G = 1;
     if (G > p.M) G = p.M;
@@ -844,7 +836,6 @@ extern "C" int hadamard_quantize_int4_cuda_bf16(void* x_int_packed_ptr, void* sc
     p.M = batch_size;
     p.quantize = 1;
     p.had_scale = __bfloat162float(__float2bfloat16_rn((float)(1.0 / sqrt((double)block))));
-    if (const char* e = getenv("QB200_HQ_DBG")) p.dbg = atoi(e);
     if (!vector_path_ok(p)) return QB200_ERR_UNSUPPORTED;
     switch (block) {
         case 64: return launch_hq_mma<64>(p, stream);

@@ -309,6 +309,12 @@ def run_b200(args):
         ops_gemm = 2.0 * m * n_local * k
         f1_bytes = 2.0 * m * k + m * k / 2 + 6.0 * m  # bf16 in + packed out + bf16 scale + int32 row sum
         int8_peak = 2.0 * peaks["bf16_tflops"]        # tcgen05 kind::i8 runs at twice the bf16 rate
+        # DRAM traffic per launch: ncu captures of the headline-size launches showed the inputs read exactly once
+        # (12.66 MB for the GEMM, 16.81 MB for the fused quantiser) and the outputs still in L2 at kernel end, so
+        # traffic = input bytes read + output bytes written back later; only reported for the captured size.
+        headline = (m, k, n_local) == (2048, 4096, 4096)
+        gemm_traffic = 12.66e6 + 2.0 * m * n_local if headline else None
+        f1_traffic = 16.81e6 + m * k / 2 + 6.0 * m if headline else None
         if args.workload == "hadamard_quantize":
             value, unit, t_main = f1_bytes / t_f1 / 1e9, "GB/s", t_f1
         elif args.workload == "gemm":
@@ -330,12 +336,14 @@ def run_b200(args):
                          "achieved": ops_gemm / t_gemm / 1e12 if t_gemm > 0 else None, "peak": int8_peak,
                          "unit": "TOPS", "frac": (ops_gemm / t_gemm / 1e12) / int8_peak if t_gemm > 0 else None,
                          "peak_source": f"2 x bf16_tflops ({peaks['bf16_tflops']}) of {peaks['source']}",
-                         "traffic": None, "us_per_launch": t_gemm * 1e6},
-            "roofline_hadamard_quantize": {"kernel": "row_kernel<128> (fused Hadamard+scale+quantise+pack)", "bound": "hbm",
+                         "traffic": gemm_traffic, "traffic_note": "12.66 MB read measured by ncu on this launch size plus the output"
+                                                                   " bytes, which L2 writes back after the kernel (profiles/)",
+                         "us_per_launch": t_gemm * 1e6},
+            "roofline_hadamard_quantize": {"kernel": "hadamard_quant_mma_kernel (fused Hadamard+scale+quantise+pack)", "bound": "hbm",
                                            "achieved": f1_bytes / t_f1 / 1e9 if t_f1 > 0 else None,
                                            "peak": peaks["hbm_gbs"], "unit": "GB/s",
                                            "frac": (f1_bytes / t_f1 / 1e9) / peaks["hbm_gbs"] if t_f1 > 0 else None,
-                                           "peak_source": f"hbm_gbs of {peaks['source']}", "traffic": None,
+                                           "peak_source": f"hbm_gbs of {peaks['source']}", "traffic": f1_traffic,
                                            "us_per_launch": t_f1 * 1e6, "algorithmic_bytes": f1_bytes},
             "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
             "wall_s_timed_region": wall,

@@ -558,15 +558,17 @@ template <int HB>
 static int launch_hq_mma(const RowParams& p, cudaStream_t stream) {
     const int units = (p.K + kUnit - 1) / kUnit;
     // units per warp, warps per row, rows per block (at most 16 warps per block)
-    int per = units >= 2 ? 2 : 1;
+    int per = units >= 2 ? 2 : 1;  // two units per warp amortise the per-row work best (measured)
     if (per > units) per = units;
     if (per != 1 && per != 2 && per != 4) per = 2;
     int W = (units + per - 1) / per;
     if (W > 8 && per < 4) { per = 4; W = (units + per - 1) / per; }
     if (W > 8) return launch_row<HB, false>(p, stream);  // very long rows: shuffle-butterfly kernel
+    // Rows per block: up to 8 warps per block, but few rows overall want small blocks so that every SM ends
+    // at the same time (a block is the unit the rows are dealt out in).
     int G = 8 / W;
-    if (G * W > 8) G = 8 / W;
     if (G < 1) G = 1;
+    while (G > 1 && (long long)p.M < 96LL * 148 * G) G >>= 1;
     if (G > p.M) G = p.M;
     const int warps = W * G;
     const size_t smem = (size_t)warps * per * kStepBytes;

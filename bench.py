@@ -48,6 +48,7 @@ def parse_args():
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--n", type=int, default=4096, help="output columns PER GPU")
     ap.add_argument("--block", type=int, default=128)
+    ap.add_argument("--exchange", default="push", choices=["push", "nccl"], help="N>1: how the column blocks are assembled")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -191,7 +192,8 @@ def run_b200(args):
     x_host, _ = synthetic_inputs(m, k, 8, seed=0)                 # activations are replicated: same seed everywhere
     x = x_host.to(dev)
     wp, ws, wa, _ = quest.preprocess_weight(w_local.to(dev), use_hadamard=True, block=args.block)
-    layer = ShardedLinear4bit((wp, ws, wa), n_total, rank, world, use_hadamard=True, block=args.block) if world > 1 else None
+    layer = (ShardedLinear4bit((wp, ws, wa), n_total, rank, world, use_hadamard=True, block=args.block,
+                               exchange=args.exchange) if world > 1 else None)
     flush = torch.zeros(L2_FLUSH_BYTES // 4, dtype=torch.int32, device=dev)
 
     a_scale = torch.empty(m, 1, dtype=torch.bfloat16, device=dev)
@@ -219,16 +221,30 @@ def run_b200(args):
             e1.record()
             quest.fused_matmul_dequantize_int4_int4t_bf16(a_packed, wp, a_rsum, wa, a_scale, ws, out)
             e2.record(); e3.record()
-        else:
+        elif args.exchange == "nccl":
             e0.record()
             lws = layer.workspaces(m, k, dev, torch.bfloat16)
-            quest.hadamard_quantize_int4(x, args.block, lws["a_int_packed"], lws["a_scale"], lws["a_int_row_sum"])
+            layer.quantize_activations(x, lws)
             e1.record()
             quest.fused_matmul_dequantize_int4_int4t_bf16_into(lws["a_int_packed"], wp, lws["a_int_row_sum"], wa,
                                                                lws["a_scale"], ws, lws["local"][:, :n_local])
             e2.record()
             dist.all_gather_into_tensor(lws["gathered"].view(-1), lws["local"].view(-1))
             lws["out"].view(m, world, -1).copy_(lws["gathered"].permute(1, 0, 2))
+            e3.record()
+        else:  # push: the GEMM epilogue stores its tiles into every rank's output; then one device-side barrier
+            e0.record()
+            lws = layer.workspaces(m, k, dev, torch.bfloat16)
+            t, hdl, ptrs = lws["symm"][lws["parity"]]
+            lws["parity"] ^= 1
+            layer.quantize_activations(x, lws)
+            e1.record()
+            off = layer.n0 * 2
+            order = [rank] + [(rank + i) % world for i in range(1, world)]
+            quest.fused_matmul_dequantize_int4_int4t_bf16_push(lws["a_int_packed"], wp, lws["a_int_row_sum"], wa,
+                                                               lws["a_scale"], ws, [ptrs[r] + off for r in order], n_total)
+            e2.record()
+            hdl.barrier(channel=0)
             e3.record()
         if timers is not None:
             timers.append((e0, e1, e2, e3))
@@ -330,7 +346,8 @@ def run_b200(args):
             "config": {"workload": f"{args.workload}: W4A4 linear M={m} K={k} N={n_local} per GPU"
                                    f" (N_total={n_total}), Hadamard block {args.block}",
                        "l2": f"L2 flushed between timed steps by writing a {L2_FLUSH_BYTES >> 20} MiB buffer",
-                       "parallelism": f"N-sharded x{world} + all-gather" if world > 1 else "single GPU",
+                       "parallelism": (f"N-sharded x{world}, " + ("epilogue pushes tiles to every GPU + barrier" if args.exchange == "push"
+                                                                       else "NCCL all-gather + interleave copy")) if world > 1 else "single GPU",
                        "inputs": "activations Student-t(nu=4) unit RMS bf16; weights N(0,0.02) quantised to packed int4"},
             "roofline": {"kernel": "gemm_i4_kernel (tcgen05 kind::i8, fused dequant epilogue)", "bound": "tensor",
                          "achieved": ops_gemm / t_gemm / 1e12 if t_gemm > 0 else None, "peak": int8_peak,

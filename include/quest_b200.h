@@ -121,6 +121,21 @@ int fused_matmul_dequantize_int4_int4t_bf16_strided_cuda(void* mat_d, long long 
                                                          cudaStream_t stream);
 
 /*
+ * Same GEMM + epilogue, with every output tile stored into n_dst (1..8) matrices of identical shape and row
+ * stride: mat_d_list[0] is normally the caller's own buffer and mat_d_list[1..] are the buffers of the other GPUs
+ * of the node, mapped into this process (peer or symmetric memory), each already offset to the caller's first
+ * output column.  The stores are ordinary (peer) stores issued from the epilogue while later tiles are still
+ * being computed; the caller synchronises the GPUs afterwards (the kernel itself does not wait for anyone).
+ * mat_d_list is a HOST array; it is copied into the kernel parameters.
+ * No counterpart in the reference.
+ */
+int fused_matmul_dequantize_int4_int4t_bf16_push_cuda(void* const* mat_d_list, int n_dst, long long ld_d,
+                                                      const void* mat_a, const void* mat_b, const void* vec_a_add,
+                                                      const void* vec_b_add, const void* vec_a_mul,
+                                                      const void* vec_b_mul, int M, int K, int N,
+                                                      cudaStream_t stream);
+
+/*
  * Fused block-Hadamard + scale + int4 quantise + pack + row-sum of bf16 activations, one pass over
  * x.  Per row: xh = bf16(H_block . x) blockwise along K (Sylvester order, entries +-bf16(block^-0.5)),
  * scale = find_scale(xh), codes = quantize(xh, scale).  Replaces the three launches of the reference's

@@ -67,6 +67,30 @@ def fused_matmul_dequantize_int4_int4t_bf16_into(
     return out_cols
 
 
+def fused_matmul_dequantize_int4_int4t_bf16_push(
+        mat_a: torch.Tensor,
+        mat_b: torch.Tensor,
+        vec_a_add: torch.Tensor,
+        vec_b_add: torch.Tensor,
+        vec_a_mul: torch.Tensor,
+        vec_b_mul: torch.Tensor,
+        dst_ptrs: list[int],
+        ld: int,
+) -> None:
+    """Same computation; every output tile is stored to each address in ``dst_ptrs`` (raw device pointers of
+    [M, ld]-strided bf16 matrices, the caller's own first, then buffers of peer GPUs mapped into this process,
+    each already offset to the caller's first column).  The caller synchronises the GPUs afterwards."""
+    import ctypes
+    assert mat_a.dtype == torch.uint8 and mat_b.dtype == torch.uint8 and vec_a_add.dtype == torch.int32 and vec_b_add.dtype == torch.int32 and vec_a_mul.dtype == torch.bfloat16 and vec_b_mul.dtype == torch.bfloat16
+    assert mat_a.is_contiguous() and mat_b.is_contiguous() and vec_a_add.is_contiguous() and vec_b_add.is_contiguous() and vec_a_mul.is_contiguous() and vec_b_mul.is_contiguous()
+    assert 1 <= len(dst_ptrs) <= 8
+    dev = _lib.require_cuda(mat_a, mat_b, vec_a_add, vec_b_add, vec_a_mul, vec_b_mul)
+    arr = (ctypes.c_void_p * len(dst_ptrs))(*dst_ptrs)
+    _call("fused_matmul_dequantize_int4_int4t_bf16_push_cuda", dev, arr, len(dst_ptrs), int(ld),
+          _lib.ptr(mat_a), _lib.ptr(mat_b), _lib.ptr(vec_a_add), _lib.ptr(vec_b_add), _lib.ptr(vec_a_mul),
+          _lib.ptr(vec_b_mul), mat_a.size(0), mat_b.size(1) * 2, mat_b.size(0), _lib.stream_of(mat_a))
+
+
 def matmul_int4_int4t_int32(
         mat_a: torch.Tensor,
         mat_b: torch.Tensor,

@@ -22,6 +22,7 @@ SIGNATURES = {
     "matmul_int4_int4t_int32_cuda": [_P, _P, _P, _I, _I, _I, _P],
     "fused_matmul_dequantize_int4_int4t_bf16_cuda": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     "fused_matmul_dequantize_int4_int4t_bf16_strided_cuda": [_P, _LL, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
+    "fused_matmul_dequantize_int4_int4t_bf16_push_cuda": [ctypes.POINTER(ctypes.c_void_p), _I, _LL, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     "hadamard_quantize_int4_cuda_bf16": [_P, _P, _P, _P, _I, _I, _I, _P],
     "hadamard_transform_cuda_bf16": [_P, _P, _I, _I, _I, _I, _P],
     "quest_b200_device_status": [ctypes.POINTER(ctypes.c_int)],

@@ -42,11 +42,14 @@ def up_to_date() -> bool:
     return all(os.path.getmtime(d) <= t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    if not force and up_to_date():
+def build(force: bool = False, verbose: bool = False, trace: bool = False, out: str = LIB_PATH) -> str:
+    """Compile the library.  ``trace=True`` adds the in-kernel timeline probes (a tuning build; give it another
+    ``out`` path so that it never replaces the product library)."""
+    if not force and not trace and up_to_date():
         return LIB_PATH
     nvcc = find_nvcc()
-    cmd = [nvcc, *NVCC_FLAGS, "-shared", "-o", LIB_PATH, *[os.path.join(CSRC, s) for s in SOURCES]]
+    cmd = [nvcc, *NVCC_FLAGS, *(["-DQB200_TRACE"] if trace else []), "-shared", "-o", out,
+           *[os.path.join(CSRC, s) for s in SOURCES]]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
@@ -56,8 +59,12 @@ def build(force: bool = False, verbose: bool = False) -> str:
         raise RuntimeError(f"nvcc failed:\n{res.stdout}\n{res.stderr}")
     if verbose:
         print(res.stderr)
-    return LIB_PATH
+    return out
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    if "--trace" in sys.argv:
+        print(build(force=True, verbose="--verbose" in sys.argv, trace=True,
+                    out=os.path.join(PKG_DIR, "libquest_b200_trace.so")))
+    else:
+        print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

@@ -36,6 +36,20 @@ namespace qb {
 
 __device__ int g_device_status = 0;
 
+#ifdef QB200_TRACE
+// Timeline probes for tuning builds (python -m quest_b200.build --trace): per CTA, globaltimer (ns) at kernel entry,
+// first MMA issue, last MMA retired, last epilogue store.  Read back with quest_b200_trace().
+__device__ unsigned long long g_trace[256][4];
+__device__ __forceinline__ unsigned long long gtime() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define QB_TRACE(slot) do { if (blockIdx.x < 256) g_trace[blockIdx.x][slot] = gtime(); } while (0)
+#else
+#define QB_TRACE(slot) do { } while (0)
+#endif
+
 // ---------------------------------------------------------------------------------------------
 // PTX wrappers
 // ---------------------------------------------------------------------------------------------
@@ -153,7 +167,9 @@ constexpr int kNumUnpackWarps = 8;
 constexpr int kNumEpilogueWarps = 4;
 constexpr int kFirstEpilogueWarp = 2;
 constexpr int kFirstUnpackWarp = kFirstEpilogueWarp + kNumEpilogueWarps;
-constexpr int kNumWarps = kFirstUnpackWarp + kNumUnpackWarps;
+constexpr int kFirstPushWarp = kFirstUnpackWarp + kNumUnpackWarps;
+constexpr int kNumPushWarps = 2;  // copy finished tiles to the other GPUs' outputs (idle on one GPU)
+constexpr int kNumWarps = kFirstPushWarp + kNumPushWarps;
 constexpr int kNumThreads = kNumWarps * 32;
 
 template <int BN>
@@ -164,8 +180,9 @@ struct Cfg {
     static constexpr int P_BYTES = ROWS * PK_ROW;
     static constexpr int U_BYTES = ROWS * U8_ROW;
     static constexpr int TMEM_COLS = (2 * BN > 256) ? 512 : 256;  // two accumulator buffers, power of two
-    static constexpr int NUM_BARS = 2 * P_STAGES + 2 * U_STAGES + 4 + 1;
-    static constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + U_STAGES * U_BYTES + P_STAGES * P_BYTES + NUM_BARS * 8 + 16;
+    static constexpr int NUM_BARS = 2 * P_STAGES + 2 * U_STAGES + 4 + 1 + 4;
+    static constexpr int VEC_BYTES = 2 * BN * 8;         // per accumulator buffer: b_add (int32) and b_mul (fp32) of the tile
+    static constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + U_STAGES * U_BYTES + P_STAGES * P_BYTES + VEC_BYTES + NUM_BARS * 8 + 16;
     // instruction descriptor: D=s32, A=B=s8, both K-major, N and M of the MMA
     static constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 };
@@ -185,46 +202,42 @@ struct EpilogueParams {
     const __nv_bfloat16* a_mul;  // [M]
     const __nv_bfloat16* b_mul;  // [N]
     int vec_ok;             // 16-byte stores are aligned for every (row, 8-column group)
+    int n_peer;             // fused only: the tile is also stored into n_peer further matrices of the same shape
+    void* peer_out[7];      // (buffers of other GPUs mapped into this address space: plain peer stores)
 };
 
 
 // Converts and stores 32 consecutive accumulators of one output row (columns col0 .. col0+31, clipped to N).
 // The accumulators carry the factor 256 of the unpack; FUSED applies the exact dequantising expression
 //   D = bf16( float(2*acc + a_add[m] + b_add[n]) * (0.5f * a_mul[m] * b_mul[n]) ),
-// otherwise the int32 accumulators are written.
+// otherwise the int32 accumulators are written.  sb_add / sb_mul point at the 32 per-column values of this
+// chunk, staged in shared memory by the epilogue warps while the tile was still being accumulated.
 template <bool FUSED>
 __device__ __forceinline__ void epilogue_store_chunk(const uint32_t (&r)[32], const EpilogueParams& ep, int row, int col0,
-                                                     int N, int a_add, float half_a_mul) {
+                                                     int N, int a_add, float half_a_mul, const int* sb_add,
+                                                     const float* sb_mul) {
     if (FUSED) {
         __nv_bfloat16* out = static_cast<__nv_bfloat16*>(ep.out) + (size_t)row * ep.ld + col0;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
             const int col = col0 + 8 * g;
-            if (ep.vec_ok && col + 8 <= N) {
-                const int4 b0 = __ldg(reinterpret_cast<const int4*>(ep.b_add + col));
-                const int4 b1 = __ldg(reinterpret_cast<const int4*>(ep.b_add + col + 4));
-                const uint4 bm = __ldg(reinterpret_cast<const uint4*>(ep.b_mul + col));
-                const int ba[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-                const uint32_t bmw[4] = {bm.x, bm.y, bm.z, bm.w};
-                uint32_t o[4];
+            const int4 b0 = *reinterpret_cast<const int4*>(sb_add + 8 * g);
+            const int4 b1 = *reinterpret_cast<const int4*>(sb_add + 8 * g + 4);
+            const float4 m0 = *reinterpret_cast<const float4*>(sb_mul + 8 * g);
+            const float4 m1 = *reinterpret_cast<const float4*>(sb_mul + 8 * g + 4);
+            const int ba[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+            const float bm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+            float v[8];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int acc0 = (int)r[8 * g + 2 * i] >> 8, acc1 = (int)r[8 * g + 2 * i + 1] >> 8;
-                    const float v0 = (float)(acc0 * 2 + a_add + ba[2 * i]) * (half_a_mul * bf16lo_to_f32(bmw[i]));
-                    const float v1 = (float)(acc1 * 2 + a_add + ba[2 * i + 1]) * (half_a_mul * bf16hi_to_f32(bmw[i]));
-                    o[i] = pack_bf16x2(v0, v1);
-                }
-                *reinterpret_cast<uint4*>(out + 8 * g) = make_uint4(o[0], o[1], o[2], o[3]);
+            for (int i = 0; i < 8; ++i)
+                v[i] = (float)(((int)r[8 * g + i] >> 8) * 2 + a_add + ba[i]) * (half_a_mul * bm[i]);
+            if (ep.vec_ok && col + 8 <= N) {
+                *reinterpret_cast<uint4*>(out + 8 * g) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]),
+                                                                    pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
             } else {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    if (col + i < N) {
-                        const int acc0 = (int)r[8 * g + i] >> 8;
-                        const float v0 = (float)(acc0 * 2 + a_add + ep.b_add[col + i]) *
-                                         (half_a_mul * bf16_to_f32(ep.b_mul[col + i]));
-                        out[8 * g + i] = __float2bfloat16_rn(v0);
-                    }
-                }
+                for (int i = 0; i < 8; ++i)
+                    if (col + i < N) out[8 * g + i] = __float2bfloat16_rn(v[i]);
             }
         }
     } else {
@@ -264,7 +277,8 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t u_base = smem_base;                                   // int8 ring, 1024-byte aligned stages
     const uint32_t p_base = u_base + C::U_STAGES * C::U_BYTES;           // packed ring
-    const uint32_t bar_base = p_base + C::P_STAGES * C::P_BYTES;         // mbarriers (8-byte aligned)
+    const uint32_t vec_base = p_base + C::P_STAGES * C::P_BYTES;         // per-column epilogue vectors (16-byte aligned)
+    const uint32_t bar_base = vec_base + C::VEC_BYTES;                   // mbarriers (8-byte aligned)
     const uint32_t full_p = bar_base;
     const uint32_t empty_p = full_p + 8 * C::P_STAGES;
     const uint32_t full_u = empty_p + 8 * C::P_STAGES;
@@ -272,7 +286,9 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const uint32_t tmem_full = empty_u + 8 * C::U_STAGES;
     const uint32_t tmem_empty = tmem_full + 16;
     const uint32_t mma_done = tmem_empty + 16;
-    const uint32_t tmem_slot = mma_done + 8;
+    const uint32_t out_ready = mma_done + 8;   // [2] epilogue -> push warps: the tile is in the local output
+    const uint32_t push_free = out_ready + 16; // [2] push warps -> epilogue
+    const uint32_t tmem_slot = push_free + 16;
     volatile uint32_t* tmem_slot_ptr =
         reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
 
@@ -285,6 +301,7 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const int num_kb = (K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
+        QB_TRACE(0);
         for (int i = 0; i < C::P_STAGES; ++i) {
             mbar_init(full_p + 8 * i, 1);
             mbar_init(empty_p + 8 * i, kNumUnpackWarps);
@@ -298,6 +315,10 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             mbar_init(tmem_empty + 8 * i, kNumEpilogueWarps);
         }
         mbar_init(mma_done, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(out_ready + 8 * i, kNumEpilogueWarps);
+            mbar_init(push_free + 8 * i, kNumPushWarps);
+        }
         fence_barrier_init();
     }
     if (warp == 1) {
@@ -349,6 +370,7 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     const uint32_t s = it % C::U_STAGES, ph = (it / C::U_STAGES) & 1u;
                     if (!(ok = mbar_wait(full_u + 8 * s, ph, 4))) break;
                     tc_fence_after();
+                    if (it == 0) QB_TRACE(1);
                     const uint32_t a_addr = u_base + s * C::U_BYTES;
                     const uint32_t b_addr = a_addr + BM * U8_ROW;
 #pragma unroll
@@ -363,42 +385,103 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             // Everything issued so far must have completed before tensor memory is released.
             umma_commit(mma_done);
             mbar_wait(mma_done, 0, 5);
+            QB_TRACE(2);
         }
     } else if (warp < kFirstUnpackWarp) {
         // ------------------------------ epilogue ------------------------------
         const int quad = warp & 3;  // tensor-memory lane quadrant this warp may read
+        const int et = threadIdx.x - kFirstEpilogueWarp * 32;  // 0 .. 127
+        uint8_t* vec_ptr = smem_raw + (vec_base - smem_u32(smem_raw));
         uint32_t local_tile = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
             const int m0 = (tile % tiles_m) * BM;
             const int n0 = (tile / tiles_m) * BN;
             const uint32_t acc = local_tile & 1u, acc_ph = (local_tile >> 1) & 1u;
-            ok = mbar_wait(tmem_full + 8 * acc, acc_ph, 6);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            tc_fence_after();
             const int row = m0 + quad * 32 + lane;
             const bool row_ok = row < M;
             int a_add = 0;
             float half_a_mul = 0.f;
-            if (FUSED && row_ok) {
-                a_add = ep.a_add[row];
-                half_a_mul = 0.5f * bf16_to_f32(ep.a_mul[row]);
+            int* sb_add = reinterpret_cast<int*>(vec_ptr + acc * (BN * 8));
+            float* sb_mul = reinterpret_cast<float*>(vec_ptr + acc * (BN * 8) + BN * 4);
+            if (FUSED) {
+                // Everything the epilogue needs besides the accumulators is fetched while the tile is still being
+                // accumulated: this tile's per-column vectors go to shared memory, the per-row pair to registers.
+                for (int c = et; c < BN; c += kNumEpilogueWarps * 32) {
+                    const bool in = n0 + c < N;
+                    sb_add[c] = in ? ep.b_add[n0 + c] : 0;
+                    sb_mul[c] = in ? bf16_to_f32(ep.b_mul[n0 + c]) : 0.f;
+                }
+                if (row_ok) {
+                    a_add = ep.a_add[row];
+                    half_a_mul = 0.5f * bf16_to_f32(ep.a_mul[row]);
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(kNumEpilogueWarps * 32) : "memory");
             }
+            ok = mbar_wait(tmem_full + 8 * acc, acc_ph, 6);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
             const uint32_t t_row = tmem_acc + ((uint32_t)(quad * 32) << 16) + acc * BN;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c0 = 0; c0 < BN; c0 += 64) {
                 if (n0 + c0 >= N) break;  // warp-uniform
-                uint32_t r[32];
-                tmem_ld32(t_row + c0, r);
+                uint32_t r0[32], r1[32];
+                tmem_ld32(t_row + c0, r0);
+                tmem_ld32(t_row + c0 + 32, r1);
                 tmem_ld_wait();
                 if (!row_ok) continue;
-                epilogue_store_chunk<FUSED>(r, ep, row, n0 + c0, N, a_add, half_a_mul);
+                epilogue_store_chunk<FUSED>(r0, ep, row, n0 + c0, N, a_add, half_a_mul, sb_add + c0, sb_mul + c0);
+                if (n0 + c0 + 32 < N)
+                    epilogue_store_chunk<FUSED>(r1, ep, row, n0 + c0 + 32, N, a_add, half_a_mul, sb_add + c0 + 32, sb_mul + c0 + 32);
             }
             // This warp has finished reading the accumulator buffer.
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tmem_empty + 8 * acc);
+            if (warp == kFirstEpilogueWarp && lane == 0) QB_TRACE(3);
+            if (FUSED && ep.n_peer > 0) {
+                // Hand the tile (now in the local output) to the push warps; at most two tiles may be pending.
+                ok = mbar_wait(push_free + 8 * acc, acc_ph ^ 1u, 11);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                __threadfence_block();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(out_ready + 8 * acc);
+            }
+        }
+    } else if (warp >= kFirstPushWarp) {
+        // ------------------------------ push warps (multi-GPU only) ------------------------------
+        // Re-read each finished tile from the local output (L2) one whole row segment per warp instruction and
+        // store it to the same place of every peer buffer: 512-byte contiguous peer stores, which NVLink moves
+        // far better than the 16-byte-per-row pieces the epilogue threads own.
+        if (FUSED && ep.n_peer > 0) {
+            const int pw = warp - kFirstPushWarp;
+            uint32_t local_tile = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+                const int m0 = (tile % tiles_m) * BM;
+                const int n0 = (tile / tiles_m) * BN;
+                const uint32_t acc = local_tile & 1u, acc_ph = (local_tile >> 1) & 1u;
+                ok = mbar_wait(out_ready + 8 * acc, acc_ph, 12);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                const int rows = min(BM, M - m0);
+                const int cols = min(BN, N - n0);  // multiple of 8 on this path (checked on the host)
+                for (int r = pw; r < rows; r += kNumPushWarps) {
+                    const size_t off = (size_t)(m0 + r) * ep.ld + n0;
+                    for (int c = lane * 8; c < cols; c += 256) {
+                        uint4 v;
+                        asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                                     : "l"(static_cast<const __nv_bfloat16*>(ep.out) + off + c));
+                        for (int pi = 0; pi < ep.n_peer; ++pi)
+                            *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(ep.peer_out[pi]) + off + c) = v;
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(push_free + 8 * acc);
+            }
         }
     } else {
         // ------------------------------ unpack warps ------------------------------
@@ -549,6 +632,11 @@ static int run_gemm(bool fused, const EpilogueParams& ep_in, const void* a, cons
     const int vec_elems = 16 / elem;
     ep.vec_ok = aligned16(ep.out) && (ep.ld % vec_elems == 0);
     if (fused) ep.vec_ok = ep.vec_ok && aligned16(ep.b_add) && aligned16(ep.b_mul);
+    for (int i = 0; i < ep.n_peer; ++i) {
+        if (ep.peer_out[i] == nullptr) return QB200_ERR_INVALID_ARGUMENT;
+        ep.vec_ok = ep.vec_ok && aligned16(ep.peer_out[i]);
+    }
+    if (ep.n_peer > 0 && (!ep.vec_ok || N % 8 != 0)) return QB200_ERR_UNSUPPORTED;  // the push path moves 16-byte pieces
     int dev = 0;
     const int sms = sm_count_of_current_device(&dev);
     if (sms <= 0) return QB200_ERR_CUDA;
@@ -580,6 +668,26 @@ extern "C" int fused_matmul_dequantize_int4_int4t_bf16_strided_cuda(void* mat_d,
     if (ld_d < N) return QB200_ERR_INVALID_ARGUMENT;
     EpilogueParams ep{};
     ep.out = mat_d;
+    ep.ld = ld_d;
+    ep.a_add = static_cast<const int32_t*>(vec_a_add);
+    ep.b_add = static_cast<const int32_t*>(vec_b_add);
+    ep.a_mul = static_cast<const __nv_bfloat16*>(vec_a_mul);
+    ep.b_mul = static_cast<const __nv_bfloat16*>(vec_b_mul);
+    return run_gemm(true, ep, mat_a, mat_b, M, K, N, stream);
+}
+
+extern "C" int fused_matmul_dequantize_int4_int4t_bf16_push_cuda(void* const* mat_d_list, int n_dst, long long ld_d,
+                                                                 const void* mat_a, const void* mat_b,
+                                                                 const void* vec_a_add, const void* vec_b_add,
+                                                                 const void* vec_a_mul, const void* vec_b_mul, int M, int K,
+                                                                 int N, cudaStream_t stream) {
+    if (mat_d_list == nullptr || n_dst < 1 || n_dst > 8) return QB200_ERR_INVALID_ARGUMENT;
+    if (M > 0 && N > 0 && (!vec_a_add || !vec_b_add || !vec_a_mul || !vec_b_mul)) return QB200_ERR_INVALID_ARGUMENT;
+    if (ld_d < N) return QB200_ERR_INVALID_ARGUMENT;
+    EpilogueParams ep{};
+    ep.out = mat_d_list[0];
+    ep.n_peer = n_dst - 1;
+    for (int i = 1; i < n_dst; ++i) ep.peer_out[i - 1] = mat_d_list[i];
     ep.ld = ld_d;
     ep.a_add = static_cast<const int32_t*>(vec_a_add);
     ep.b_add = static_cast<const int32_t*>(vec_b_add);
@@ -622,3 +730,10 @@ extern "C" const char* quest_b200_error_string(int status) {
 }
 
 extern "C" int quest_b200_version(void) { return 100; }
+
+#ifdef QB200_TRACE
+extern "C" int quest_b200_trace(unsigned long long* out, int n_ctas) {
+    if (cudaDeviceSynchronize() != cudaSuccess) return QB200_ERR_CUDA;
+    return cuda_status(cudaMemcpyFromSymbol(out, g_trace, sizeof(unsigned long long) * 4 * (n_ctas < 256 ? n_ctas : 256)));
+}
+#endif

@@ -6,6 +6,12 @@ so all ranks hold identical codes), runs the fused GEMM for its N/g output colum
 blocks are assembled with one all-gather.  Per element the arithmetic is the single-GPU arithmetic, so
 the assembled output is bit-identical to the 1-GPU result.  The reference has no multi-GPU inference
 path; this is the exchange step the sharding needs and nothing more.
+
+Two exchange modes:
+  "push"  the GEMM epilogue stores every finished tile straight into the [M, N_total] output buffer of every GPU
+          (buffers in symmetric memory, plain peer stores over NVLink, issued while later tiles are still being
+          computed), followed by one device-side barrier.  No collective kernel, no interleaving copy.
+  "nccl"  each rank computes into a local block, NCCL all-gathers the blocks and one copy interleaves them.
 """
 from __future__ import annotations
 
@@ -41,7 +47,10 @@ class ShardedLinear4bit:
     """
 
     def __init__(self, w_shard: tuple[torch.Tensor, torch.Tensor, torch.Tensor], n_total: int, rank: int, world: int,
-                 group=None, use_hadamard: bool = True, block: int = 128):
+                 group=None, use_hadamard: bool = True, block: int = 128, exchange: str = "nccl"):
+        if exchange not in ("nccl", "push"):
+            raise ValueError(f"unknown exchange mode {exchange!r}")
+        self.exchange = exchange
         self.w_int_packed, self.w_scale, self.w_add = w_shard
         self.n_total, self.rank, self.world, self.group = n_total, rank, world, group
         self.use_hadamard, self.block = use_hadamard, block
@@ -62,10 +71,36 @@ class ShardedLinear4bit:
         quest.fused_matmul_dequantize_int4_int4t_bf16_into(ws["a_int_packed"], self.w_int_packed, ws["a_int_row_sum"],
                                                            self.w_add, ws["a_scale"], self.w_scale, out_cols)
 
+    def quantize_activations(self, x: torch.Tensor, ws: dict) -> None:
+        if self.use_hadamard:
+            quest.hadamard_quantize_int4(x, self.block, ws["a_int_packed"], ws["a_scale"], ws["a_int_row_sum"])
+        else:
+            quest.find_scale_int4(x, ws["a_scale"])
+            quest.quantize_int4(x, ws["a_scale"], None, ws["a_int_packed"], ws["a_int_row_sum"])
+
+    def symmetric_outputs(self, m: int, device, dtype) -> list:
+        """Two [M, N_total] output buffers in symmetric memory (alternated call by call, so that one barrier per
+        call is enough: a buffer is rewritten only after every rank has passed the barrier of the call in between,
+        which in stream order lies behind that rank's readers of the older result).  Collective: every rank must
+        make its first call with a given M together."""
+        import torch.distributed._symmetric_memory as symm_mem
+        group = self.group if self.group is not None else dist.group.WORLD
+        out = []
+        for _ in range(2):
+            t = symm_mem.empty((m, self.n_total), dtype=dtype, device=device)
+            hdl = symm_mem.rendezvous(t, group)
+            ptrs = [int(p) for p in hdl.buffer_ptrs]
+            if len(ptrs) != self.world:
+                raise RuntimeError("symmetric memory group does not match the sharding world size")
+            out.append((t, hdl, ptrs))
+        return out
+
     def workspaces(self, m: int, k: int, device, dtype) -> dict:
         key = (m, k, str(device))
         if key not in self._ws:
             self._ws[key] = dict(
+                symm=self.symmetric_outputs(m, device, dtype) if (self.exchange == "push" and self.world > 1) else None,
+                parity=0,
                 a_scale=torch.empty(m, 1, dtype=dtype, device=device),
                 a_int_packed=torch.empty(m, k // 2, dtype=torch.uint8, device=device),
                 a_int_row_sum=torch.empty(m, 1, dtype=torch.int32, device=device),
@@ -85,6 +120,17 @@ class ShardedLinear4bit:
         if not gather:
             self.compute_shard(x, out[:, self.n0:self.n1], ws)
             return out
+        if self.exchange == "push":
+            t, hdl, ptrs = ws["symm"][ws["parity"]]
+            ws["parity"] ^= 1
+            self.quantize_activations(x, ws)
+            off = self.n0 * t.element_size()
+            order = [self.rank] + [(self.rank + i) % self.world for i in range(1, self.world)]
+            quest.fused_matmul_dequantize_int4_int4t_bf16_push(
+                ws["a_int_packed"], self.w_int_packed, ws["a_int_row_sum"], self.w_add, ws["a_scale"], self.w_scale,
+                [ptrs[r] + off for r in order], self.n_total)
+            hdl.barrier(channel=0)  # every rank's tiles have landed everywhere
+            return t
         # NCCL all-gather wants one contiguous, equal-sized block per rank: gather [g, M, width], then
         # interleave the column blocks into the row-major [M, N_total] result.
         self.compute_shard(x, ws["local"][:, :self.n1 - self.n0], ws)

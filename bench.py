@@ -264,6 +264,7 @@ def run_b200(args):
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
+    barrier()  # rank 0 waited for the clock sampler's first sample: start the timed region together
     timers = []
     wall0 = time.perf_counter()
     for _ in range(args.steps):
@@ -276,6 +277,10 @@ def run_b200(args):
     t_f1 = sum(e0.elapsed_time(e1) for e0, e1, _, _ in timers) / len(timers) * 1e-3
     t_gemm = sum(e1.elapsed_time(e2) for _, e1, e2, _ in timers) / len(timers) * 1e-3
     t_step = sum(e0.elapsed_time(e3) for e0, _, _, e3 in timers) / len(timers) * 1e-3
+    if os.environ.get("QB200_BENCH_DEBUG"):
+        t_x = sum(e2.elapsed_time(e3) for _, _, e2, e3 in timers) / len(timers) * 1e-3
+        print(f"[rank {rank}] step {t_step * 1e6:.1f} us = f1 {t_f1 * 1e6:.1f} + gemm {t_gemm * 1e6:.1f} + exchange {t_x * 1e6:.1f};"
+              f" wall/step {wall / args.steps * 1e6:.1f} us", file=sys.stderr, flush=True)
     if world > 1:
         tt = torch.tensor([t_step, t_f1, t_gemm], dtype=torch.float64, device=dev)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)

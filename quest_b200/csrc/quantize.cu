@@ -309,30 +309,43 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a
 
 // Thread-block shape: G row groups x W warps.  The W warps of a group share one row (UNITS 1024-element
 // units per warp); the block walks over batches of G rows.  Everything that is per row rather than per
-// element (summing the partial sums, sqrt, rounding the scale, its reciprocal, the clamp bounds, the final
-// row sum) is done once per batch by warp 0, one row per lane, so it costs a few instructions per row
-// instead of a hundred per thread.
-struct HqRowConst {
-    float inv_s;
-    uint32_t lo2, hi2;  // clamp bounds -8s and ~7.5s as bf16 pairs
-    uint32_t pad;
-};
+// element (summing the partial sums, sqrt, rounding the scale, its reciprocal, the clamp bounds) is a short
+// float chain that every warp evaluates for its own row right after the one barrier that publishes the partial
+// sums; the final row sums are written one batch later by warp 0.
+#ifdef QB200_TRACE
+// Tuning builds only: earliest block start, latest start, earliest end and latest end (globaltimer, ns) of the last launch.
+__device__ unsigned long long g_hq_trace[4] = {~0ull, 0ull, ~0ull, 0ull};
+__device__ __forceinline__ unsigned long long hq_gtime() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#endif
 
 template <int HB, int UNITS>
 __global__ void __launch_bounds__(256, UNITS == 1 ? 4 : (UNITS == 2 ? 3 : 2))
-hadamard_quant_mma_kernel(const RowParams p, const int W, const int G) {
+hadamard_quant_mma_kernel(const RowParams p, const int W, const int G, const int nbuf) {
     extern __shared__ __align__(16) uint8_t hq_smem[];
-    __shared__ float part_ssq[8];
-    __shared__ int part_rs[8];
-    __shared__ HqRowConst row_const[8];
+    __shared__ float part_ssq[2][8];  // indexed by batch parity: one barrier per batch is enough
+    __shared__ int part_rs[2][8];
 
+#ifdef QB200_TRACE
+    if (threadIdx.x == 0) {
+        const unsigned long long t = hq_gtime();
+        atomicMin(&g_hq_trace[0], t);
+        atomicMax(&g_hq_trace[1], t);
+    }
+#endif
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const int grp = warp / W;      // row group of this warp
     const int wig = warp - grp * W;  // warp index within the group
     const int g = lane >> 2, tig = lane & 3;
     const int K = p.K, M = p.M;
-    const uint32_t smem_w = (uint32_t)__cvta_generic_to_shared(hq_smem) + warp * (UNITS * kStepBytes);
+    // nbuf = 2: the next row's copies are in flight while this row is processed.  nbuf = 1 (every row batch of the
+    // launch is resident at once, nothing to prefetch): half the shared memory, twice the blocks per SM.
+    const int step_bytes = nbuf * kStepIn;
+    const uint32_t smem_w = (uint32_t)__cvta_generic_to_shared(hq_smem) + warp * (UNITS * step_bytes);
     const int num_batches = (M + G - 1) / G;
 
     // Copies of this warp's units of one row into input buffer `buf` (16 bytes per lane and instruction).
@@ -342,7 +355,7 @@ hadamard_quant_mma_kernel(const RowParams p, const int W, const int G) {
 #pragma unroll
             for (int u = 0; u < UNITS; ++u) {
                 const int unit = u * W + wig;
-                const uint32_t in_base = smem_w + u * kStepBytes + buf * kStepIn;
+                const uint32_t in_base = smem_w + u * step_bytes + buf * kStepIn;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int c = j * 32 + lane;  // 16-byte chunk within the unit
@@ -376,15 +389,16 @@ hadamard_quant_mma_kernel(const RowParams p, const int W, const int G) {
         }
     }
 
-    int prev_batch = -1;
+    int prev_batch = -1, last_par = 0;
     for (int it = 0; batch < num_batches; batch += gridDim.x, ++it) {
-        const int buf = it & 1;
+        const int buf = nbuf == 2 ? (it & 1) : 0;
         const int row = batch * G + grp;
         const int next = batch + gridDim.x;
-        if (next < num_batches) {
+        if (nbuf == 2 && next < num_batches) {
             issue_row(next * G + grp, buf ^ 1);
             asm volatile("cp.async.wait_group 1;" ::: "memory");
         } else {
+            if (nbuf == 1 && it > 0) issue_row(row, 0);  // single buffer: fetch this row now (the staging reads are done)
             asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncwarp();
@@ -393,7 +407,7 @@ hadamard_quant_mma_kernel(const RowParams p, const int W, const int G) {
         float ssq = 0.f;
 #pragma unroll
         for (int u = 0; u < UNITS; ++u) {
-            const uint32_t in_base = smem_w + u * kStepBytes + buf * kStepIn;
+            const uint32_t in_base = smem_w + u * step_bytes + buf * kStepIn;
             float f[8][4];
 #pragma unroll
             for (int t = 0; t < 4; ++t) {
@@ -448,50 +462,41 @@ hadamard_quant_mma_kernel(const RowParams p, const int W, const int G) {
         }
 #pragma unroll
         for (int m = 16; m > 0; m >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, m);
-        if (lane == 0) part_ssq[warp] = ssq;
-        __syncthreads();  // B1: partial sums of this batch (and row-sum partials of the previous one) are in place
+        const int par = it & 1;
+        if (lane == 0) part_ssq[par][warp] = ssq;
+        __syncthreads();  // the partial sums of this batch (and the row-sum partials of the previous one) are in place
 
-        if (warp == 0 && lane < G) {
-            const int r = batch * G + lane;
-            if (r < M) {
-                double tot = 0.0;
-                for (int i = 0; i < W; ++i) tot += (double)part_ssq[lane * W + i];
-                const __nv_bfloat16 sb = __float2bfloat16_rn(quest_scale_from_mean_square((float)(tot / (double)K)));
-                p.scale_out[r] = sb;
-                const float s_f = bf16_to_f32(sb);
-                const uint32_t lo1 = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(-8.f * s_f));
-                const uint32_t hi1 = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(7.5f * s_f));
-                HqRowConst rc;
-                rc.inv_s = __frcp_rn(s_f);
-                rc.lo2 = lo1 | (lo1 << 16);
-                rc.hi2 = hi1 | (hi1 << 16);
-                rc.pad = 0;
-                row_const[lane] = rc;
-            }
-            if (prev_batch >= 0 && p.row_sum != nullptr) {
-                const int pr = prev_batch * G + lane;
-                if (pr < M) {
-                    int t2 = 0;
-                    for (int i = 0; i < W; ++i) t2 += part_rs[lane * W + i];
-                    p.row_sum[pr] = t2 >> 4;  // exact: every term is a multiple of 16
-                }
-            }
-        }
-        __syncthreads();  // B2: the row constants are published
-
-        // ---- quantise, stage, store ----
+        // Every warp derives its row's constants itself (a short float chain, W partial sums): no second barrier
+        // and nobody waits for a designated warp.  Warp 0 additionally publishes the scales and finishes the row
+        // sums of the previous batch, off everyone's critical path.
+        double tot = 0.0;
+        for (int i = 0; i < W; ++i) tot += (double)part_ssq[par][grp * W + i];
+        const __nv_bfloat16 sb = __float2bfloat16_rn(quest_scale_from_mean_square(__fdiv_rn((float)tot, (float)K)));
+        const float s_f = bf16_to_f32(sb);
+        const float inv_s = __frcp_rn(s_f);
         // Saturation is done on the bf16 pairs before the divide: x is clamped to [-8s, ~7.5s], both bounds
         // exact or safely inside [7s, 8s), so floor(x/s) lands in [-8, 7] without integer min/max, and the
         // code is simply the low nibble of the magic-number sum.
-        const HqRowConst rc = row_const[grp];
-        const float inv_s = rc.inv_s;
-        const uint32_t lo2 = rc.lo2, hi2 = rc.hi2;
+        const uint32_t lo1 = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(-8.f * s_f));
+        const uint32_t hi1 = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(7.5f * s_f));
+        const uint32_t lo2 = lo1 | (lo1 << 16), hi2 = hi1 | (hi1 << 16);
+        if (wig == 0 && lane == 0 && row < M) p.scale_out[row] = sb;
+        if (warp == 0 && lane < G && prev_batch >= 0 && p.row_sum != nullptr) {
+            const int pr = prev_batch * G + lane;
+            if (pr < M) {
+                int t2 = 0;
+                for (int i = 0; i < W; ++i) t2 += part_rs[par ^ 1][lane * W + i];
+                p.row_sum[pr] = t2 >> 4;  // exact: every term is a multiple of 16
+            }
+        }
+
+        // ---- quantise, stage, store ----
         const bool vec_store = (K & 31) == 0;
         int rs16 = 0;
 #pragma unroll
         for (int u = 0; u < UNITS; ++u) {
             const int unit = u * W + wig;
-            const uint32_t out_base = smem_w + u * kStepBytes + buf * kStepIn;  // input already consumed
+            const uint32_t out_base = smem_w + u * step_bytes + buf * kStepIn;  // input already consumed
 #pragma unroll
             for (int pr = 0; pr < 4; ++pr) {  // rows a = 2pr and 2pr + 1: eight codes -> one 32-bit word
                 uint32_t ub[8];
@@ -536,16 +541,24 @@ hadamard_quant_mma_kernel(const RowParams p, const int W, const int G) {
         }
 #pragma unroll
         for (int m = 16; m > 0; m >>= 1) rs16 += __shfl_xor_sync(0xffffffffu, rs16, m);
-        if (lane == 0) part_rs[warp] = rs16;
+        if (lane == 0) part_rs[par][warp] = rs16;
         prev_batch = batch;
+        last_par = par;
     }
     // row sums of the last batch
     __syncthreads();
+#ifdef QB200_TRACE
+    if (threadIdx.x == 0) {
+        const unsigned long long t = hq_gtime();
+        atomicMin(&g_hq_trace[2], t);
+        atomicMax(&g_hq_trace[3], t);
+    }
+#endif
     if (warp == 0 && lane < G && prev_batch >= 0 && p.row_sum != nullptr) {
         const int pr = prev_batch * G + lane;
         if (pr < M) {
             int t2 = 0;
-            for (int i = 0; i < W; ++i) t2 += part_rs[lane * W + i];
+            for (int i = 0; i < W; ++i) t2 += part_rs[last_par][lane * W + i];
             p.row_sum[pr] = t2 >> 4;
         }
     }
@@ -571,8 +584,8 @@ static int launch_hq_mma(const RowParams& p, cudaStream_t stream) {
     while (G > 1 && (long long)p.M < 96LL * 148 * G) G >>= 1;
     if (G > p.M) G = p.M;
     const int warps = W * G;
-    const size_t smem = (size_t)warps * per * kStepBytes;
-    if (smem > kMaxDynSmem) return launch_row<HB, false>(p, stream);
+    const long long batches = ((long long)p.M + G - 1) / G;
+    if ((size_t)warps * per * kStepBytes > kMaxDynSmem) return launch_row<HB, false>(p, stream);
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) != cudaSuccess) return QB200_ERR_CUDA;
     {
@@ -585,7 +598,7 @@ static int launch_hq_mma(const RowParams& p, cudaStream_t stream) {
     // Persistent grid: as many blocks as fit on the device at once (bounded by the number of row batches).
     // The caches are per kernel instantiation (index `which`) and per device.
     static bool attr_done[3][64] = {{false}};
-    static int occ_cache[3][64][9] = {{{0}}};
+    static int occ_cache[3][64][9][2] = {{{{0}}}};
     auto launch = [&](auto kernel, int which) -> int {
         const bool dev_ok = dev >= 0 && dev < 64;
         if (!(dev_ok && attr_done[which][dev])) {
@@ -595,18 +608,26 @@ static int launch_hq_mma(const RowParams& p, cudaStream_t stream) {
             }
             if (dev_ok) attr_done[which][dev] = true;
         }
-        int occ = dev_ok ? occ_cache[which][dev][warps] : 0;
-        if (occ <= 0) {
-            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, 32 * warps, smem) != cudaSuccess || occ <= 0) {
-                cudaGetLastError();
-                occ = 1;
+        auto occupancy = [&](int nb) {
+            int occ = dev_ok ? occ_cache[which][dev][warps][nb - 1] : 0;
+            if (occ <= 0) {
+                if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, 32 * warps, (size_t)warps * per * nb * kStepIn) != cudaSuccess || occ <= 0) {
+                    cudaGetLastError();
+                    occ = 1;
+                }
+                if (dev_ok) occ_cache[which][dev][warps][nb - 1] = occ;
             }
-            if (dev_ok) occ_cache[which][dev][warps] = occ;
+            return occ;
+        };
+        // If every row batch fits on the device at once there is nothing to prefetch: use one input buffer.
+        int nbuf = 2;
+        long long grid = (long long)sms * occupancy(2);
+        if (batches > grid && batches <= (long long)sms * occupancy(1)) {
+            nbuf = 1;
+            grid = (long long)sms * occupancy(1);
         }
-        const long long batches = ((long long)p.M + G - 1) / G;
-        long long grid = (long long)sms * occ;
         if (grid > batches) grid = batches;
-        kernel<<<(unsigned)grid, 32 * warps, smem, stream>>>(p, W, G);
+        kernel<<<(unsigned)grid, 32 * warps, (size_t)warps * per * nbuf * kStepIn, stream>>>(p, W, G, nbuf);
         return launch_status();
     };
     if (per == 1) return launch(hadamard_quant_mma_kernel<HB, 1>, 0);
@@ -781,6 +802,15 @@ __global__ void __launch_bounds__(256) add_mul_vv_scalar_kernel(__nv_bfloat16* _
 // C ABI
 // -------------------------------------------------------------------------------------------------
 using namespace qb;
+
+#ifdef QB200_TRACE
+extern "C" int quest_b200_hq_trace(unsigned long long* out) {
+    if (cudaDeviceSynchronize() != cudaSuccess) return QB200_ERR_CUDA;
+    if (cudaMemcpyFromSymbol(out, g_hq_trace, sizeof(unsigned long long) * 4) != cudaSuccess) return QB200_ERR_CUDA;
+    const unsigned long long init[4] = {~0ull, 0ull, ~0ull, 0ull};
+    return cuda_status(cudaMemcpyToSymbol(g_hq_trace, init, sizeof(init)));
+}
+#endif
 
 extern "C" int find_scale_int4_cuda_bf16(void* scale_ptr, const void* x_ptr, int group_size, int batch_size,
                                          cudaStream_t stream) {

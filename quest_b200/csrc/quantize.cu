@@ -322,6 +322,20 @@ __device__ __forceinline__ unsigned long long hq_gtime() {
 }
 #endif
 
+// Packed fp32 pairs (sm_100 executes add/sub/mul/fma on two floats per instruction).
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pk2(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpk2(f32x2 v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) { f32x2 r; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
+__device__ __forceinline__ f32x2 sub2(f32x2 a, f32x2 b) { f32x2 r; asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) { f32x2 r; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
+__device__ __forceinline__ f32x2 add2_rd(f32x2 a, f32x2 b) { f32x2 r; asm("add.rm.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) { f32x2 r; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c)); return r; }
+
 template <int HB, int UNITS>
 __global__ void __launch_bounds__(256, UNITS == 1 ? 4 : (UNITS == 2 ? 3 : 2))
 hadamard_quant_mma_kernel(const RowParams p, const int W, const int G, const int nbuf) {
@@ -404,11 +418,11 @@ hadamard_quant_mma_kernel(const RowParams p, const int W, const int G, const int
         __syncwarp();
 
         uint32_t v[UNITS][16];  // v[u][2a + nu]: elements 16a + 4tig + 2nu (+1) of block g of the unit
-        float ssq = 0.f;
+        f32x2 ssq2 = 0ull;
 #pragma unroll
         for (int u = 0; u < UNITS; ++u) {
             const uint32_t in_base = smem_w + u * step_bytes + buf * kStepIn;
-            float f[8][4];
+            f32x2 f[8][2];  // f[a][h]: elements 16a + 4tig + 2h, +1 of block g, as packed float pairs
 #pragma unroll
             for (int t = 0; t < 4; ++t) {
                 uint32_t a[4];
@@ -417,10 +431,8 @@ hadamard_quant_mma_kernel(const RowParams p, const int W, const int G, const int
                 for (int nu = 0; nu < 2; ++nu) {
                     float d[4];
                     mma_bf16_16816(d, a, bfrag[nu][0], bfrag[nu][1]);
-                    f[2 * t][2 * nu] = d[0];
-                    f[2 * t][2 * nu + 1] = d[1];
-                    f[2 * t + 1][2 * nu] = d[2];
-                    f[2 * t + 1][2 * nu + 1] = d[3];
+                    f[2 * t][nu] = pk2(d[0], d[1]);
+                    f[2 * t + 1][nu] = pk2(d[2], d[3]);
                 }
             }
             // remaining index bits 4.. of the block: butterflies over the row index a (in registers)
@@ -430,10 +442,10 @@ hadamard_quant_mma_kernel(const RowParams p, const int W, const int G, const int
                 for (int a = 0; a < 8; ++a) {
                     if ((a & s) == 0) {
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const float x0 = f[a][j], x1 = f[a + s][j];
-                            f[a][j] = x0 + x1;
-                            f[a + s][j] = x0 - x1;
+                        for (int h = 0; h < 2; ++h) {
+                            const f32x2 x0 = f[a][h], x1 = f[a + s][h];
+                            f[a][h] = add2(x0, x1);
+                            f[a + s][h] = sub2(x0, x1);
                         }
                     }
                 }
@@ -443,22 +455,33 @@ hadamard_quant_mma_kernel(const RowParams p, const int W, const int G, const int
 #pragma unroll
                 for (int a = 0; a < 8; ++a)
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const float pv = __shfl_xor_sync(0xffffffffu, f[a][j], 4);
-                        f[a][j] = fmaf(f[a][j], sgn, pv);
+                    for (int h = 0; h < 2; ++h) {
+                        float x0, x1;
+                        unpk2(f[a][h], x0, x1);
+                        const float p0 = __shfl_xor_sync(0xffffffffu, x0, 4);
+                        const float p1 = __shfl_xor_sync(0xffffffffu, x1, 4);
+                        f[a][h] = pk2(fmaf(x0, sgn, p0), fmaf(x1, sgn, p1));
                     }
             }
 #pragma unroll
-            for (int a = 0; a < 8; ++a) {
-                v[u][2 * a] = pack_bf16x2(f[a][0], f[a][1]);
-                v[u][2 * a + 1] = pack_bf16x2(f[a][2], f[a][3]);
-            }
+            for (int a = 0; a < 8; ++a)
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    float x0, x1;
+                    unpk2(f[a][h], x0, x1);
+                    v[u][2 * a + h] = pack_bf16x2(x0, x1);
+                }
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-                const float x0 = bf16lo_to_f32(v[u][i]), x1 = bf16hi_to_f32(v[u][i]);
-                ssq = fmaf(x0, x0, ssq);
-                ssq = fmaf(x1, x1, ssq);
+                const f32x2 xx = pk2(bf16lo_to_f32(v[u][i]), bf16hi_to_f32(v[u][i]));
+                ssq2 = fma2(xx, xx, ssq2);
             }
+        }
+        float ssq;
+        {
+            float s0, s1;
+            unpk2(ssq2, s0, s1);
+            ssq = s0 + s1;
         }
 #pragma unroll
         for (int m = 16; m > 0; m >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, m);
@@ -480,6 +503,7 @@ hadamard_quant_mma_kernel(const RowParams p, const int W, const int G, const int
         const uint32_t lo1 = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(-8.f * s_f));
         const uint32_t hi1 = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(7.5f * s_f));
         const uint32_t lo2 = lo1 | (lo1 << 16), hi2 = hi1 | (hi1 << 16);
+        const f32x2 inv_s2 = pk2(inv_s, inv_s), magic2 = pk2(kFloorMagic, kFloorMagic);
         if (wig == 0 && lane == 0 && row < M) p.scale_out[row] = sb;
         if (warp == 0 && lane < G && prev_batch >= 0 && p.row_sum != nullptr) {
             const int pr = prev_batch * G + lane;
@@ -503,8 +527,14 @@ hadamard_quant_mma_kernel(const RowParams p, const int W, const int G, const int
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const uint32_t c = clamp_bf16x2(v[u][4 * pr + i], lo2, hi2);
-                    ub[2 * i] = floor_quotient_bits(bf16lo_to_f32(c), inv_s);
-                    ub[2 * i + 1] = floor_quotient_bits(bf16hi_to_f32(c), inv_s);
+                    float y0, y1;
+                    unpk2(mul2(pk2(bf16lo_to_f32(c), bf16hi_to_f32(c)), inv_s2), y0, y1);
+                    // nudge towards +inf by |y| * 2^-13 (see floor_quotient), then floor through the magic-number sum
+                    const f32x2 fl = add2_rd(pk2(fmaf(fabsf(y0), 1.220703125e-4f, y0), fmaf(fabsf(y1), 1.220703125e-4f, y1)), magic2);
+                    float u0, u1;
+                    unpk2(fl, u0, u1);
+                    ub[2 * i] = __float_as_uint(u0);
+                    ub[2 * i + 1] = __float_as_uint(u1);
                 }
                 // ub[0..3] = row 2pr elements 0..3, ub[4..7] = row 2pr+1 elements 0..3; code = low nibble
                 const uint32_t ev = __byte_perm(__byte_perm(ub[0], ub[2], 0x0040), __byte_perm(ub[4], ub[6], 0x0040), 0x5410);

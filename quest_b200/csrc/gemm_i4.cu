@@ -468,15 +468,24 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 if (!ok) break;
                 const int rows = min(BM, M - m0);
                 const int cols = min(BN, N - n0);  // multiple of 8 on this path (checked on the host)
-                for (int r = pw; r < rows; r += kNumPushWarps) {
-                    const size_t off = (size_t)(m0 + r) * ep.ld + n0;
+                // eight rows per pass: all loads of a pass are in flight before the first store is issued
+                for (int r0 = pw * 8; r0 < rows; r0 += kNumPushWarps * 8) {
                     for (int c = lane * 8; c < cols; c += 256) {
-                        uint4 v;
-                        asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];"
-                                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                                     : "l"(static_cast<const __nv_bfloat16*>(ep.out) + off + c));
-                        for (int pi = 0; pi < ep.n_peer; ++pi)
-                            *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(ep.peer_out[pi]) + off + c) = v;
+                        uint4 v[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            if (r0 + j < rows) {
+                                const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(ep.out) + (size_t)(m0 + r0 + j) * ep.ld + n0 + c;
+                                asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                             : "=r"(v[j].x), "=r"(v[j].y), "=r"(v[j].z), "=r"(v[j].w) : "l"(src));
+                            }
+                        }
+                        for (int pi = 0; pi < ep.n_peer; ++pi) {
+                            __nv_bfloat16* dstp = static_cast<__nv_bfloat16*>(ep.peer_out[pi]) + (size_t)(m0 + r0) * ep.ld + n0 + c;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                if (r0 + j < rows) *reinterpret_cast<uint4*>(dstp + (size_t)j * ep.ld) = v[j];
+                        }
                     }
                 }
                 __syncwarp();

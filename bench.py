@@ -43,7 +43,9 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="linear", choices=["linear", "gemm", "hadamard_quantize"])
+    ap.add_argument("--workload", default="linear", choices=["linear", "gemm", "hadamard_quantize", "prefill"])
+    ap.add_argument("--batch", type=int, default=16, help="prefill workload: sequences")
+    ap.add_argument("--seq", type=int, default=1024, help="prefill workload: tokens per sequence")
     ap.add_argument("--m", type=int, default=2048)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--n", type=int, default=4096, help="output columns PER GPU")
@@ -380,8 +382,32 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
+def run_prefill(args):
+    """End-to-end prefill of the 800M-shaped decoder (d=2048, 16 layers, 16 heads, SwiGLU 5632, vocab 32000) with
+    random-init weights: bf16 linears vs W4A4 linears (with Hadamard) vs no-op linears, eager and CUDA graph."""
+    from quest_b200.prefill import Decoder, DecoderConfig, swap_linears, prefill_time
+    dev = torch.device("cuda", 0)
+    cfg = DecoderConfig(sequence_length=max(1024, args.seq))
+    out = {"metric": "prefill ms (batch x seq tokens through the decoder body)", "unit": "ms", "higher_is_better": False,
+           "config": {"workload": f"prefill d={cfg.n_embd} L={cfg.n_layer} heads={cfg.n_head} ffn={cfg.ffn} "
+                                  f"batch={args.batch} seq={args.seq}", "data": "uniform random token ids, random-init weights"}}
+    for mode in ("bf16", "int4", "noop"):
+        torch.manual_seed(0)
+        model = swap_linears(Decoder(cfg).to(device=dev, dtype=torch.bfloat16).eval(), mode, use_hadamard=True)
+        eager_ms, graph_ms, _ = prefill_time(model, args.batch, args.seq, n_warmup=args.warmup, n_iter=min(args.steps, 20))
+        out[mode] = {"eager_ms": eager_ms, "graph_ms": graph_ms, "tokens_per_s": args.batch * args.seq / (min(eager_ms, graph_ms) * 1e-3)}
+        del model
+        torch.cuda.empty_cache()
+    out["value"] = min(out["int4"]["eager_ms"], out["int4"]["graph_ms"])
+    out["speedup_vs_bf16"] = min(out["bf16"]["eager_ms"], out["bf16"]["graph_ms"]) / out["value"]
+    print(json.dumps(out))
+
+
 def main():
     args = parse_args()
+    if args.workload == "prefill":
+        run_prefill(args)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -363,3 +363,35 @@ def test_cuda_graph_capture_and_replay():
     torch.cuda.synchronize()
     assert gt["c"].cpu().equal(O.matmul_int4_int4t_int32(a, b))
     assert gt["y"].equal(quest.linear_forward(x.to(DEV), wp, ws, wa, use_hadamard=True))
+
+
+# ------------------------------------------------------------------ prefill of a small decoder ---------
+def test_prefill_decoder_module_swap_and_graph():
+    """Small Llama-style decoder: the swapped model tracks the bf16 one within W4A4 noise, a CUDA-graph replay
+    reproduces the eager result bit for bit, and each swapped linear equals the oracle layer on its own input."""
+    from quest_b200.prefill import Decoder, DecoderConfig, swap_linears, prefill_time
+    torch.manual_seed(0)
+    cfg = DecoderConfig(n_embd=256, n_layer=2, n_head=4, ffn=768, vocab_size=512, sequence_length=64)
+    ref_model = Decoder(cfg).to(device=DEV, dtype=torch.bfloat16).eval()
+    q_model = Decoder(cfg).to(device=DEV, dtype=torch.bfloat16).eval()
+    q_model.load_state_dict(ref_model.state_dict())
+    first_w = q_model.transformer.h[0].attn.c_attn.weight.data.clone()
+    swap_linears(q_model, "int4", use_hadamard=True)
+    assert all(isinstance(m, quest.Linear4bit) for m in [q_model.transformer.h[0].attn.c_attn, q_model.transformer.h[1].mlp.c_proj])
+    idx = torch.randint(0, cfg.vocab_size, (4, 64), generator=torch.Generator().manual_seed(1)).to(DEV)
+    with torch.inference_mode():
+        y_ref, y_q = ref_model(idx), q_model(idx)
+        # one swapped linear against the oracle layer, same input
+        x_in = ref_model.transformer.h[0].ln_1(ref_model.transformer.wte(idx)).flatten(end_dim=-2)
+        got = q_model.transformer.h[0].attn.c_attn(x_in)
+    wp, ws, wa, _ = O.preprocess_weight(first_w.cpu(), use_hadamard=True)
+    want = O.linear_forward(x_in.cpu(), wp, ws, wa, use_hadamard=True)
+    assert (got.cpu() != want).float().mean() < 0.02 and ((got.cpu().float() - want.float()).norm() / want.float().norm()) < 2e-3
+    rel = ((y_q.float() - y_ref.float()).norm() / y_ref.float().norm()).item()
+    assert rel < 0.5, rel
+    eager_ms, graph_ms, y_graph = prefill_time(q_model, 4, 64, n_warmup=2, n_iter=3, seed=1)
+    assert eager_ms > 0 and graph_ms > 0
+    assert y_graph.equal(y_q)
+    noop = swap_linears(Decoder(cfg).to(device=DEV, dtype=torch.bfloat16).eval(), "noop")
+    with torch.inference_mode():
+        assert noop(idx).shape == y_ref.shape

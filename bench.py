@@ -196,6 +196,18 @@ def run_b200(args):
     wp, ws, wa, _ = quest.preprocess_weight(w_local.to(dev), use_hadamard=True, block=args.block)
     layer = (ShardedLinear4bit((wp, ws, wa), n_total, rank, world, use_hadamard=True, block=args.block,
                                exchange=args.exchange) if world > 1 else None)
+    if layer is not None and args.exchange == "push":
+        # Symmetric memory needs peer access between the GPUs; if it cannot be set up, say so and use NCCL.
+        try:
+            layer.workspaces(m, k, dev, torch.bfloat16)
+            ok = torch.ones(1, device=dev)
+        except Exception as e:  # noqa: BLE001
+            print(f"[rank {rank}] push exchange unavailable ({e!r}); using the NCCL all-gather", file=sys.stderr)
+            ok = torch.zeros(1, device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if ok.item() == 0:
+            args.exchange = "nccl"
+            layer = ShardedLinear4bit((wp, ws, wa), n_total, rank, world, use_hadamard=True, block=args.block, exchange="nccl")
     flush = torch.zeros(L2_FLUSH_BYTES // 4, dtype=torch.int32, device=dev)
 
     a_scale = torch.empty(m, 1, dtype=torch.bfloat16, device=dev)

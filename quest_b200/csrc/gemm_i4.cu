@@ -618,15 +618,19 @@ static int launch_gemm(const EpilogueParams& ep, const void* a, const void* b, i
 
 
 static int pick_bn(int M, int N, int sms) {
-    // Prefer the 128x256 tile (more reuse per byte of shared-memory traffic) unless the narrower tile
-    // fills the SMs clearly better.
-    auto eff = [&](int bn) {
+    // Per 128-K stage a CTA needs about max(616, 3 * (128 + BN)) cycles: the four MMAs take ~616 cycles whatever
+    // N is, the unpack moves 3 shared-memory wavefronts per operand row.  Wide tiles amortise the A rows; narrow
+    // ones fill more SMs when there are few tiles (small M).  Pick the width with the shortest estimated time.
+    int best = 256;
+    long long best_t = -1;
+    for (int bn : {256, 128, 64}) {
         const long long tiles = (long long)((M + BM - 1) / BM) * ((N + bn - 1) / bn);
         const long long waves = (tiles + sms - 1) / sms;
-        return (double)tiles * bn / (double)(waves * sms * 256);
-    };
-    if (N <= 128) return 128;
-    return eff(128) > 1.15 * eff(256) ? 128 : 256;
+        const long long per_stage = 3 * (128 + bn) > 616 ? 3 * (128 + bn) : 616;
+        const long long t = waves * per_stage;
+        if (best_t < 0 || t < best_t) { best_t = t; best = bn; }
+    }
+    return best;
 }
 
 static int run_gemm(bool fused, const EpilogueParams& ep_in, const void* a, const void* b, int M, int K, int N,
@@ -650,10 +654,14 @@ static int run_gemm(bool fused, const EpilogueParams& ep_in, const void* a, cons
     const int sms = sm_count_of_current_device(&dev);
     if (sms <= 0) return QB200_ERR_CUDA;
     const int bn = pick_bn(M, N, sms);
-    if (fused) return bn == 256 ? launch_gemm<256, true>(ep, a, b, M, K, N, sms, dev, stream)
-                                : launch_gemm<128, true>(ep, a, b, M, K, N, sms, dev, stream);
-    return bn == 256 ? launch_gemm<256, false>(ep, a, b, M, K, N, sms, dev, stream)
-                     : launch_gemm<128, false>(ep, a, b, M, K, N, sms, dev, stream);
+    if (fused) {
+        if (bn == 256) return launch_gemm<256, true>(ep, a, b, M, K, N, sms, dev, stream);
+        if (bn == 128) return launch_gemm<128, true>(ep, a, b, M, K, N, sms, dev, stream);
+        return launch_gemm<64, true>(ep, a, b, M, K, N, sms, dev, stream);
+    }
+    if (bn == 256) return launch_gemm<256, false>(ep, a, b, M, K, N, sms, dev, stream);
+    if (bn == 128) return launch_gemm<128, false>(ep, a, b, M, K, N, sms, dev, stream);
+    return launch_gemm<64, false>(ep, a, b, M, K, N, sms, dev, stream);
 }
 
 }  // namespace qb

@@ -395,3 +395,19 @@ def test_prefill_decoder_module_swap_and_graph():
     noop = swap_linears(Decoder(cfg).to(device=DEV, dtype=torch.bfloat16).eval(), "noop")
     with torch.inference_mode():
         assert noop(idx).shape == y_ref.shape
+
+
+def test_push_entry_point_copies_tiles_to_every_destination():
+    """The multi-GPU entry point on ONE GPU: two further local buffers stand in for the peers' outputs.  Every
+    destination must receive exactly the column block, and nothing outside it."""
+    m, k, n, n_total = 300, 1024, 264, 1056
+    a, b = random_packed(m, k, 61).to(DEV), random_packed(n, k, 62).to(DEV)
+    a_add, a_mul, b_add, b_mul = [t.to(DEV) for t in epilogue_inputs(m, n, 63)]
+    bufs = [torch.zeros(m, n_total, dtype=torch.bfloat16, device=DEV) for _ in range(3)]
+    col0 = 528
+    ptrs = [t.data_ptr() + col0 * 2 for t in bufs]
+    quest.fused_matmul_dequantize_int4_int4t_bf16_push(a, b, a_add, b_add, a_mul, b_mul, ptrs, n_total)
+    want = O.fused_matmul_dequantize_int4_int4t_bf16(a.cpu(), b.cpu(), a_add.cpu(), b_add.cpu(), a_mul.cpu(), b_mul.cpu())
+    for t in bufs:
+        assert t[:, col0:col0 + n].cpu().equal(want)
+        assert int(t[:, :col0].abs().sum()) == 0 and int(t[:, col0 + n:].abs().sum()) == 0

@@ -43,7 +43,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="linear", choices=["linear", "gemm", "hadamard_quantize", "prefill"])
+    ap.add_argument("--workload", default="linear", choices=["linear", "gemm", "hadamard_quantize", "prefill", "sweep"])
     ap.add_argument("--batch", type=int, default=16, help="prefill workload: sequences")
     ap.add_argument("--seq", type=int, default=1024, help="prefill workload: tokens per sequence")
     ap.add_argument("--m", type=int, default=2048)
@@ -415,10 +415,71 @@ def run_prefill(args):
     print(json.dumps(out))
 
 
+def run_sweep(args):
+    """The single-GPU shape sweeps: W4A4 linear at K=4096, N in {4096, 11008, 12288}, M in {1, 16, 128, 2048, 8192}
+    (fused quantiser + GEMM, each timed with events, L2 flushed between runs) and the Hadamard+quantise bandwidth
+    sweep M in {1, 256, 4096, 65536} x K in {4096, 8192, 14336} x block in {64, 128, 256}.  One JSON object."""
+    import quest_b200 as quest
+    dev = torch.device("cuda", 0)
+    peaks = measured_peaks()
+    flush = torch.zeros(L2_FLUSH_BYTES // 4, dtype=torch.int32, device=dev)
+
+    def timed(fn, iters=15, warm=4):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(iters):
+            flush.add_(1)
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record(); fn(); e.record()
+            torch.cuda.synchronize()
+            ts.append(s.elapsed_time(e) * 1e-3)
+        ts.sort()
+        return ts[len(ts) // 2]
+
+    g = torch.Generator().manual_seed(0)
+    linear = []
+    for n in (4096, 11008, 12288):
+        w = (0.02 * torch.randn(n, 4096, generator=g)).to(torch.bfloat16).to(dev)
+        wp, ws, wa, _ = quest.preprocess_weight(w, use_hadamard=True)
+        for m in (1, 16, 128, 2048, 8192):
+            x = torch.randn(m, 4096, generator=g).to(torch.bfloat16).to(dev)
+            sc = torch.empty(m, 1, dtype=torch.bfloat16, device=dev)
+            pk = torch.empty(m, 2048, dtype=torch.uint8, device=dev)
+            rs = torch.empty(m, 1, dtype=torch.int32, device=dev)
+            out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+            t_q = timed(lambda: quest.hadamard_quantize_int4(x, 128, pk, sc, rs))
+            t_g = timed(lambda: quest.fused_matmul_dequantize_int4_int4t_bf16(pk, wp, rs, wa, sc, ws, out))
+            ops = 2.0 * m * n * 4096
+            gemm_bytes = m * 2048 + n * 2048 + 2.0 * m * n + 6.0 * (m + n)
+            linear.append({"M": m, "N": n, "K": 4096, "quantize_us": t_q * 1e6, "gemm_us": t_g * 1e6,
+                           "gemm_tops": ops / t_g / 1e12, "gemm_gbs": gemm_bytes / t_g / 1e9,
+                           "layer_tops": ops / (t_q + t_g) / 1e12})
+    hq = []
+    for k in (4096, 8192, 14336):
+        for m in (1, 256, 4096, 65536):
+            x = torch.randn(m, k, generator=g).to(torch.bfloat16).to(dev) if m * k < (1 << 28) else \
+                torch.randn(m, k, device=dev).to(torch.bfloat16)
+            sc = torch.empty(m, 1, dtype=torch.bfloat16, device=dev)
+            pk = torch.empty(m, k // 2, dtype=torch.uint8, device=dev)
+            rs = torch.empty(m, 1, dtype=torch.int32, device=dev)
+            for block in (64, 128, 256):
+                t = timed(lambda: quest.hadamard_quantize_int4(x, block, pk, sc, rs), iters=9, warm=3)
+                nbytes = 2.0 * m * k + m * k / 2 + 6.0 * m
+                hq.append({"M": m, "K": k, "block": block, "us": t * 1e6, "gbs": nbytes / t / 1e9,
+                           "frac_of_hbm": nbytes / t / 1e9 / peaks["hbm_gbs"]})
+            del x, pk
+    print(json.dumps({"workload": "sweep", "peaks": peaks, "linear": linear, "hadamard_quantize": hq}))
+
+
 def main():
     args = parse_args()
     if args.workload == "prefill":
         run_prefill(args)
+        return
+    if args.workload == "sweep":
+        run_sweep(args)
         return
     if args.impl == "reference":
         run_reference(args)

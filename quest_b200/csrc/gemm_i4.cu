@@ -547,6 +547,307 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
 
 // ---------------------------------------------------------------------------------------------
+// The 256 x 256 tile kernel
+// ---------------------------------------------------------------------------------------------
+// The kernel above is bound by shared-memory traffic, not by the tensor core: per 128-K stage every operand row
+// costs a TMA write, a 64-byte read, a 128-byte int8 write and the MMA's own reads.  A 256 x 256 output tile
+// (two 128-row accumulators that share the B operand) halves the B traffic per unit of work.  Its price: the two
+// accumulators fill all 512 columns of tensor memory, so the epilogue of a tile cannot overlap the MMAs of the
+// next one (its TMA and unpack still do), and shared memory holds only two int8 stages.  The host picks this
+// kernel where the estimated time is shorter (large M and N).
+namespace wide {
+constexpr int TM = 256, TN = 256;
+constexpr int P_STAGES = 3, U_STAGES = 2;
+constexpr int P_BYTES = (TM + TN) * PK_ROW;   // 32 KB packed per stage
+constexpr int U_BYTES = (TM + TN) * U8_ROW;   // 64 KB int8 per stage
+constexpr int kEpiWarps = 8, kFirstEpi = 2;
+constexpr int kUnpackWarps = 8, kFirstUnpack = kFirstEpi + kEpiWarps;
+constexpr int kPushWarps = 2, kFirstPush = kFirstUnpack + kUnpackWarps;
+constexpr int kWarps = kFirstPush + kPushWarps;
+constexpr int kThreads = kWarps * 32;
+constexpr int VEC_BYTES = TN * 8;
+constexpr int NUM_BARS = 2 * P_STAGES + 2 * U_STAGES + 2 + 1 + 4;
+constexpr int LAYOUT_BYTES = U_STAGES * U_BYTES + P_STAGES * P_BYTES + VEC_BYTES + NUM_BARS * 8 + 16;
+constexpr int SMEM_BYTES = 232448;  // all the shared memory one CTA can have; the layout needs a 1024-byte aligned start
+static_assert(LAYOUT_BYTES <= SMEM_BYTES, "layout does not fit");
+constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}  // namespace wide
+
+template <bool FUSED>
+__global__ void __launch_bounds__(wide::kThreads, 1)
+gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const EpilogueParams ep, const int M, const int N, const int K) {
+    using namespace wide;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_base = smem_u32(smem_raw);
+    const uint32_t smem_base = (raw_base + 1023u) & ~1023u;
+    if (smem_base - raw_base + LAYOUT_BYTES > SMEM_BYTES) {  // uniform over the CTA: nothing has been set up yet
+        if (threadIdx.x == 0) atomicCAS(&g_device_status, 0, (13 << 8) | QB200_ERR_DEVICE_TIMEOUT);
+        return;
+    }
+    const uint32_t u_base = smem_base;
+    const uint32_t p_base = u_base + U_STAGES * U_BYTES;
+    const uint32_t vec_base = p_base + P_STAGES * P_BYTES;
+    const uint32_t bar_base = vec_base + VEC_BYTES;
+    const uint32_t full_p = bar_base;
+    const uint32_t empty_p = full_p + 8 * P_STAGES;
+    const uint32_t full_u = empty_p + 8 * P_STAGES;
+    const uint32_t empty_u = full_u + 8 * U_STAGES;
+    const uint32_t tmem_full = empty_u + 8 * U_STAGES;
+    const uint32_t tmem_empty = tmem_full + 8;
+    const uint32_t mma_done = tmem_empty + 8;
+    const uint32_t out_ready = mma_done + 8;    // [2]
+    const uint32_t push_free = out_ready + 16;  // [2]
+    const uint32_t tmem_slot = push_free + 16;
+    volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - raw_base));
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int tiles_m = (M + TM - 1) / TM;
+    const int tiles_n = (N + TN - 1) / TN;
+    const int num_tiles = tiles_m * tiles_n;
+    const int num_kb = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        QB_TRACE(0);
+        for (int i = 0; i < P_STAGES; ++i) {
+            mbar_init(full_p + 8 * i, 1);
+            mbar_init(empty_p + 8 * i, kUnpackWarps);
+        }
+        for (int i = 0; i < U_STAGES; ++i) {
+            mbar_init(full_u + 8 * i, kUnpackWarps);
+            mbar_init(empty_u + 8 * i, 1);
+        }
+        mbar_init(tmem_full, 1);
+        mbar_init(tmem_empty, kEpiWarps);
+        mbar_init(mma_done, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(out_ready + 8 * i, kEpiWarps);
+            mbar_init(push_free + 8 * i, kPushWarps);
+        }
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_acc = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            tma_prefetch_desc(&tmap_a);
+            tma_prefetch_desc(&tmap_b);
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % tiles_m) * TM;
+                const int n0 = (tile / tiles_m) * TN;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const uint32_t s = it % P_STAGES, ph = (it / P_STAGES) & 1u;
+                    if (!(ok = mbar_wait(empty_p + 8 * s, ph ^ 1u, 1))) break;
+                    mbar_arrive_expect_tx(full_p + 8 * s, P_BYTES);
+                    const uint32_t dst = p_base + s * P_BYTES;
+                    tma_load_2d(dst, &tmap_a, kb * PK_ROW, m0, full_p + 8 * s);
+                    tma_load_2d(dst + TM * PK_ROW, &tmap_b, kb * PK_ROW, n0, full_p + 8 * s);
+                }
+            }
+            const uint32_t pending = it < (uint32_t)P_STAGES ? it : (uint32_t)P_STAGES;
+            for (uint32_t j = 0; j < pending; ++j) {
+                const uint32_t i2 = it - 1 - j;
+                mbar_wait(full_p + 8 * (i2 % P_STAGES), (i2 / P_STAGES) & 1u, 2);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            uint32_t it = 0, local_tile = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+                const int m0 = (tile % tiles_m) * TM;
+                const int halves = (m0 + 128 < M) ? 2 : 1;  // the lower accumulator is skipped when its rows are all outside M
+                if (!(ok = mbar_wait(tmem_empty, (local_tile & 1u) ^ 1u, 3))) break;
+                tc_fence_after();
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const uint32_t s = it % U_STAGES, ph = (it / U_STAGES) & 1u;
+                    if (!(ok = mbar_wait(full_u + 8 * s, ph, 4))) break;
+                    tc_fence_after();
+                    if (it == 0) QB_TRACE(1);
+                    const uint32_t a_addr = u_base + s * U_BYTES;
+                    const uint32_t b_addr = a_addr + TM * U8_ROW;
+#pragma unroll
+                    for (int j = 0; j < BK / 32; ++j) {
+                        const uint64_t db = make_smem_desc(b_addr + 32 * j);
+                        umma_i8(tmem_acc, make_smem_desc(a_addr + 32 * j), db, IDESC, (kb | j) != 0 ? 1u : 0u);
+                        if (halves == 2)
+                            umma_i8(tmem_acc + TN, make_smem_desc(a_addr + 128 * U8_ROW + 32 * j), db, IDESC, (kb | j) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(empty_u + 8 * s);
+                }
+                if (ok) umma_commit(tmem_full);
+            }
+            umma_commit(mma_done);
+            mbar_wait(mma_done, 0, 5);
+            QB_TRACE(2);
+        }
+    } else if (warp < kFirstUnpack) {
+        // ------------------------------ epilogue ------------------------------
+        const int quad = warp & 3;                  // tensor-memory lane quadrant this warp may read
+        const int half = (warp - kFirstEpi) >> 2;   // which accumulator (rows 0-127 or 128-255 of the tile)
+        const int et = threadIdx.x - kFirstEpi * 32;  // 0 .. 255
+        uint8_t* vec_ptr = smem_raw + (vec_base - raw_base);
+        int* sb_add = reinterpret_cast<int*>(vec_ptr);
+        float* sb_mul = reinterpret_cast<float*>(vec_ptr + TN * 4);
+        uint32_t local_tile = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+            const int m0 = (tile % tiles_m) * TM;
+            const int n0 = (tile / tiles_m) * TN;
+            const uint32_t slot = local_tile & 1u, slot_ph = (local_tile >> 1) & 1u;
+            const int row = m0 + half * 128 + quad * 32 + lane;
+            const bool row_ok = row < M;
+            int a_add = 0;
+            float half_a_mul = 0.f;
+            if (FUSED) {
+                // all epilogue warps are done with the previous tile's vectors before they are overwritten
+                asm volatile("bar.sync 1, %0;" ::"n"(kEpiWarps * 32) : "memory");
+                {
+                    const bool in = n0 + et < N;
+                    sb_add[et] = in ? ep.b_add[n0 + et] : 0;
+                    sb_mul[et] = in ? bf16_to_f32(ep.b_mul[n0 + et]) : 0.f;
+                }
+                if (row_ok) {
+                    a_add = ep.a_add[row];
+                    half_a_mul = 0.5f * bf16_to_f32(ep.a_mul[row]);
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(kEpiWarps * 32) : "memory");
+            }
+            ok = mbar_wait(tmem_full, local_tile & 1u, 6);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t t_row = tmem_acc + ((uint32_t)(quad * 32) << 16) + half * TN;
+            if (m0 + half * 128 < M) {  // warp-uniform: otherwise this accumulator was not computed
+#pragma unroll 1
+                for (int c0 = 0; c0 < TN; c0 += 64) {
+                    if (n0 + c0 >= N) break;
+                    uint32_t r0[32], r1[32];
+                    tmem_ld32(t_row + c0, r0);
+                    tmem_ld32(t_row + c0 + 32, r1);
+                    tmem_ld_wait();
+                    if (!row_ok) continue;
+                    epilogue_store_chunk<FUSED>(r0, ep, row, n0 + c0, N, a_add, half_a_mul, sb_add + c0, sb_mul + c0);
+                    if (n0 + c0 + 32 < N)
+                        epilogue_store_chunk<FUSED>(r1, ep, row, n0 + c0 + 32, N, a_add, half_a_mul, sb_add + c0 + 32, sb_mul + c0 + 32);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tmem_empty);
+            if (warp == kFirstEpi && lane == 0) QB_TRACE(3);
+            if (FUSED && ep.n_peer > 0) {
+                ok = mbar_wait(push_free + 8 * slot, slot_ph ^ 1u, 11);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                __threadfence_block();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(out_ready + 8 * slot);
+            }
+        }
+    } else if (warp >= kFirstPush) {
+        // ------------------------------ push warps (multi-GPU only) ------------------------------
+        if (FUSED && ep.n_peer > 0) {
+            const int pw = warp - kFirstPush;
+            uint32_t local_tile = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+                const int m0 = (tile % tiles_m) * TM;
+                const int n0 = (tile / tiles_m) * TN;
+                const uint32_t slot = local_tile & 1u, slot_ph = (local_tile >> 1) & 1u;
+                ok = mbar_wait(out_ready + 8 * slot, slot_ph, 12);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                const int rows = min(TM, M - m0);
+                const int cols = min(TN, N - n0);
+                for (int r0 = pw * 8; r0 < rows; r0 += kPushWarps * 8) {
+                    for (int c = lane * 8; c < cols; c += 256) {
+                        uint4 v[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            if (r0 + j < rows) {
+                                const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(ep.out) + (size_t)(m0 + r0 + j) * ep.ld + n0 + c;
+                                asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                             : "=r"(v[j].x), "=r"(v[j].y), "=r"(v[j].z), "=r"(v[j].w) : "l"(src));
+                            }
+                        }
+                        for (int pi = 0; pi < ep.n_peer; ++pi) {
+                            __nv_bfloat16* dstp = static_cast<__nv_bfloat16*>(ep.peer_out[pi]) + (size_t)(m0 + r0) * ep.ld + n0 + c;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                if (r0 + j < rows) *reinterpret_cast<uint4*>(dstp + (size_t)j * ep.ld) = v[j];
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(push_free + 8 * slot);
+            }
+        }
+    } else {
+        // ------------------------------ unpack warps ------------------------------
+        const int t = threadIdx.x - kFirstUnpack * 32;  // 0 .. 255
+        uint32_t it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const uint32_t ps = it % P_STAGES, pph = (it / P_STAGES) & 1u;
+                const uint32_t us = it % U_STAGES, uph = (it / U_STAGES) & 1u;
+                ok = mbar_wait(full_p + 8 * ps, pph, 7) && mbar_wait(empty_u + 8 * us, uph ^ 1u, 8);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                const uint32_t src = p_base + ps * P_BYTES;
+                const uint32_t dst = u_base + us * U_BYTES;
+                constexpr int ITEMS = (TM + TN) * 4 / (kUnpackWarps * 32);  // 8
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    uint4 pk[ITEMS / 2];
+#pragma unroll
+                    for (int i = 0; i < ITEMS / 2; ++i) {
+                        const int item = t + (h * (ITEMS / 2) + i) * kUnpackWarps * 32;
+                        pk[i] = lds128(src + (item >> 2) * PK_ROW + (item & 3) * 16);
+                    }
+#pragma unroll
+                    for (int i = 0; i < ITEMS / 2; ++i) {
+                        const int item = t + (h * (ITEMS / 2) + i) * kUnpackWarps * 32;
+                        const int r = item >> 2, c = item & 3;
+                        uint4 lo, hi;
+                        unpack_x16(pk[i], lo, hi);
+                        const uint32_t rowaddr = dst + r * U8_ROW;
+                        sts128(rowaddr + (((2 * c) ^ (r & 7)) << 4), lo);
+                        sts128(rowaddr + (((2 * c + 1) ^ (r & 7)) << 4), hi);
+                    }
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(full_u + 8 * us);
+                    mbar_arrive(empty_p + 8 * ps);
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_acc, 512);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -617,18 +918,55 @@ static int launch_gemm(const EpilogueParams& ep, const void* a, const void* b, i
 }
 
 
-static int pick_bn(int M, int N, int sms) {
-    // Per 128-K stage a CTA needs about max(616, 3 * (128 + BN)) cycles: the four MMAs take ~616 cycles whatever
-    // N is, the unpack moves 3 shared-memory wavefronts per operand row.  Wide tiles amortise the A rows; narrow
-    // ones fill more SMs when there are few tiles (small M).  Pick the width with the shortest estimated time.
+template <bool FUSED>
+static int launch_gemm_wide(const EpilogueParams& ep, const void* a, const void* b, int M, int K, int N, int sms, int dev,
+                            cudaStream_t stream) {
+    static bool attr_set[64] = {false};
+    auto kernel = gemm_i4_wide_kernel<FUSED>;
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, wide::SMEM_BYTES) != cudaSuccess)
+            return QB200_ERR_CUDA;
+        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
+    CUtensorMap ma, mb;
+    int st = make_packed_map(&ma, a, M, K, wide::TM);
+    if (st != QB200_OK) return st;
+    st = make_packed_map(&mb, b, N, K, wide::TN);
+    if (st != QB200_OK) return st;
+    const int tiles = ((M + wide::TM - 1) / wide::TM) * ((N + wide::TN - 1) / wide::TN);
+    const int grid = tiles < sms ? tiles : sms;
+    kernel<<<grid, wide::kThreads, wide::SMEM_BYTES, stream>>>(ma, mb, ep, M, N, K);
+    return launch_status();
+}
+
+// Tile shapes: 64, 128, 256 = gemm_i4_kernel<BN> (128-row tiles); kWideTile = gemm_i4_wide_kernel (256 x 256).
+constexpr int kWideTile = 512;
+
+static int pick_tile(int M, int N, int K, int sms) {
+    // Estimated cycles.  Per 128-K stage a CTA of the 128-row kernel needs about max(616, 3 * (128 + BN)) cycles:
+    // the four MMAs take ~616 cycles whatever N is, the unpack moves 3 shared-memory wavefronts per operand row.
+    // Wide tiles amortise the A rows; narrow ones fill more SMs when there are few tiles (small M).  The 256 x 256
+    // kernel shares B between two accumulators (3 * 512 cycles for twice the work) but exposes one epilogue per tile.
+    // QB200_GEMM_TILE = 64 | 128 | 256 | 512 in the environment forces a shape (tests and tuning).
+    if (const char* e = getenv("QB200_GEMM_TILE")) {
+        const int v = atoi(e);
+        if (v == 64 || v == 128 || v == 256 || v == kWideTile) return v;
+    }
+    const long long kb = (K + BK - 1) / BK;
     int best = 256;
     long long best_t = -1;
     for (int bn : {256, 128, 64}) {
         const long long tiles = (long long)((M + BM - 1) / BM) * ((N + bn - 1) / bn);
         const long long waves = (tiles + sms - 1) / sms;
         const long long per_stage = 3 * (128 + bn) > 616 ? 3 * (128 + bn) : 616;
-        const long long t = waves * per_stage;
+        const long long t = waves * kb * per_stage + 24 * bn;  // + the last tile's epilogue
         if (best_t < 0 || t < best_t) { best_t = t; best = bn; }
+    }
+    {
+        const long long tiles = (long long)((M + wide::TM - 1) / wide::TM) * ((N + wide::TN - 1) / wide::TN);
+        const long long waves = (tiles + sms - 1) / sms;
+        const long long t = waves * (kb * 1536 + 7000);
+        if (t < best_t) { best_t = t; best = kWideTile; }
     }
     return best;
 }
@@ -653,7 +991,10 @@ static int run_gemm(bool fused, const EpilogueParams& ep_in, const void* a, cons
     int dev = 0;
     const int sms = sm_count_of_current_device(&dev);
     if (sms <= 0) return QB200_ERR_CUDA;
-    const int bn = pick_bn(M, N, sms);
+    const int bn = pick_tile(M, N, K, sms);
+    if (bn == kWideTile)
+        return fused ? launch_gemm_wide<true>(ep, a, b, M, K, N, sms, dev, stream)
+                     : launch_gemm_wide<false>(ep, a, b, M, K, N, sms, dev, stream);
     if (fused) {
         if (bn == 256) return launch_gemm<256, true>(ep, a, b, M, K, N, sms, dev, stream);
         if (bn == 128) return launch_gemm<128, true>(ep, a, b, M, K, N, sms, dev, stream);

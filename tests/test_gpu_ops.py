@@ -256,6 +256,31 @@ def test_fused_matmul_dequantize_bit_exact(m, k, n):
     assert got.dtype == torch.bfloat16 and got.cpu().equal(ref)
 
 
+@pytest.mark.parametrize("tile", [64, 128, 256, 512])
+@pytest.mark.parametrize("m,k,n", [(300, 1024, 520), (129, 256, 257), (256, 512, 256), (1, 128, 8), (1100, 384, 1544)])
+def test_every_tile_shape_is_bit_exact(tile, m, k, n, monkeypatch):
+    """QB200_GEMM_TILE forces one tile shape (512 = the 256 x 256 kernel): each must give the same bits on full,
+    ragged and many-tiles-per-CTA shapes, for the int32 and the fused entry points."""
+    monkeypatch.setenv("QB200_GEMM_TILE", str(tile))
+    a, b = random_packed(m, k, 41), random_packed(n, k, 42)
+    ad, bd = a.to(DEV), b.to(DEV)
+    assert quest.matmul_int4_int4t_int32(ad, bd).cpu().equal(O.matmul_int4_int4t_int32(a, b))
+    a_add, a_mul, b_add, b_mul = epilogue_inputs(m, n, 43)
+    ref = O.fused_matmul_dequantize_int4_int4t_bf16(a, b, a_add, b_add, a_mul, b_mul)
+    got = quest.fused_matmul_dequantize_int4_int4t_bf16(ad, bd, a_add.to(DEV), b_add.to(DEV), a_mul.to(DEV), b_mul.to(DEV))
+    assert got.cpu().equal(ref)
+
+
+def test_wide_tile_kernel_full_size_against_cublas(monkeypatch):
+    """The 256 x 256 kernel at a size with several tiles per CTA (M=4096, K=2048, N=10240 -> 640 tiles)."""
+    monkeypatch.setenv("QB200_GEMM_TILE", "512")
+    m, k, n = 4096, 2048, 10240
+    ad, bd = random_packed(m, k, 51).to(DEV), random_packed(n, k, 52).to(DEV)
+    c = quest.matmul_int4_int4t_int32(ad, bd)
+    ref = torch._int_mm(quest.unpack_int4(ad), quest.unpack_int4(bd).t().contiguous())
+    assert c.equal(ref)
+
+
 def test_fused_into_column_slice():
     m, k, n, n_total = 96, 512, 128, 512
     a, b = random_packed(m, k, 31), random_packed(n, k, 32)

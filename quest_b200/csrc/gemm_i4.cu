@@ -201,7 +201,7 @@ struct EpilogueParams {
     const int32_t* b_add;   // [N]
     const __nv_bfloat16* a_mul;  // [M]
     const __nv_bfloat16* b_mul;  // [N]
-    int vec_ok;             // 16-byte stores are aligned for every (row, 8-column group)
+    int vec_ok;             // 1: 16-byte stores are aligned for every (row, 16-byte column group); 2: 32-byte ones too
     int n_peer;             // fused only: the tile is also stored into n_peer further matrices of the same shape
     void* peer_out[7];      // (buffers of other GPUs mapped into this address space: plain peer stores)
 };
@@ -212,15 +212,20 @@ struct EpilogueParams {
 //   D = bf16( float(2*acc + a_add[m] + b_add[n]) * (0.5f * a_mul[m] * b_mul[n]) ),
 // otherwise the int32 accumulators are written.  sb_add / sb_mul point at the 32 per-column values of this
 // chunk, staged in shared memory by the epilogue warps while the tile was still being accumulated.
+__device__ __forceinline__ void stg256(void* p, const uint32_t* w) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]),
+                 "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+}
+
 template <bool FUSED>
 __device__ __forceinline__ void epilogue_store_chunk(const uint32_t (&r)[32], const EpilogueParams& ep, int row, int col0,
                                                      int N, int a_add, float half_a_mul, const int* sb_add,
                                                      const float* sb_mul) {
     if (FUSED) {
         __nv_bfloat16* out = static_cast<__nv_bfloat16*>(ep.out) + (size_t)row * ep.ld + col0;
+        uint32_t w[16];  // the 32 results as bf16 pairs
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-            const int col = col0 + 8 * g;
             const int4 b0 = *reinterpret_cast<const int4*>(sb_add + 8 * g);
             const int4 b1 = *reinterpret_cast<const int4*>(sb_add + 8 * g + 4);
             const float4 m0 = *reinterpret_cast<const float4*>(sb_mul + 8 * g);
@@ -229,19 +234,40 @@ __device__ __forceinline__ void epilogue_store_chunk(const uint32_t (&r)[32], co
             const float bm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
             float v[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
-                v[i] = (float)(((int)r[8 * g + i] >> 8) * 2 + a_add + ba[i]) * (half_a_mul * bm[i]);
-            if (ep.vec_ok && col + 8 <= N) {
-                *reinterpret_cast<uint4*>(out + 8 * g) = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]),
-                                                                    pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
-            } else {
+            for (int i = 0; i < 8; ++i)  // acc >> 7 == 2 * (acc >> 8): the accumulator is a multiple of 256
+                v[i] = (float)(((int)r[8 * g + i] >> 7) + a_add + ba[i]) * (half_a_mul * bm[i]);
 #pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    if (col + i < N) out[8 * g + i] = __float2bfloat16_rn(v[i]);
+            for (int i = 0; i < 4; ++i) w[4 * g + i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+        }
+        if (ep.vec_ok == 2 && col0 + 32 <= N) {
+            stg256(out, w);
+            stg256(out + 16, w + 8);
+        } else {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                const int col = col0 + 8 * g;
+                if (ep.vec_ok && col + 8 <= N) {
+                    *reinterpret_cast<uint4*>(out + 8 * g) = make_uint4(w[4 * g], w[4 * g + 1], w[4 * g + 2], w[4 * g + 3]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        if (col + i < N)
+                            reinterpret_cast<uint16_t*>(out)[8 * g + i] = (uint16_t)(w[4 * g + i / 2] >> (16 * (i & 1)));
+                }
             }
         }
     } else {
         int32_t* out = static_cast<int32_t*>(ep.out) + (size_t)row * ep.ld + col0;
+        if (ep.vec_ok == 2 && col0 + 32 <= N) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                uint32_t w[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) w[i] = (uint32_t)((int)r[8 * g + i] >> 8);
+                stg256(out + 8 * g, w);
+            }
+            return;
+        }
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
             const int col = col0 + 4 * g;
@@ -982,10 +1008,10 @@ static int run_gemm(bool fused, const EpilogueParams& ep_in, const void* a, cons
     const int elem = fused ? 2 : 4;
     const int vec_elems = 16 / elem;
     ep.vec_ok = aligned16(ep.out) && (ep.ld % vec_elems == 0);
-    if (fused) ep.vec_ok = ep.vec_ok && aligned16(ep.b_add) && aligned16(ep.b_mul);
+    if (ep.vec_ok && (reinterpret_cast<uintptr_t>(ep.out) & 31u) == 0 && ep.ld % (2 * vec_elems) == 0) ep.vec_ok = 2;
     for (int i = 0; i < ep.n_peer; ++i) {
         if (ep.peer_out[i] == nullptr) return QB200_ERR_INVALID_ARGUMENT;
-        ep.vec_ok = ep.vec_ok && aligned16(ep.peer_out[i]);
+        if (!aligned16(ep.peer_out[i])) ep.vec_ok = 0;
     }
     if (ep.n_peer > 0 && (!ep.vec_ok || N % 8 != 0)) return QB200_ERR_UNSUPPORTED;  // the push path moves 16-byte pieces
     int dev = 0;

@@ -185,6 +185,8 @@ def run_b200(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        # NCCL prints its version banner on stdout at NCCL_DEBUG=VERSION/INFO; stdout carries the one JSON line
+        os.environ["NCCL_DEBUG"] = os.environ.get("QB200_NCCL_DEBUG", "WARN")
         dist.init_process_group("nccl", device_id=dev)
     peaks = measured_peaks()
 
@@ -345,10 +347,10 @@ def run_b200(args):
         f1_bytes = 2.0 * m * k + m * k / 2 + 6.0 * m  # bf16 in + packed out + bf16 scale + int32 row sum
         int8_peak = 2.0 * peaks["bf16_tflops"]        # tcgen05 kind::i8 runs at twice the bf16 rate
         # DRAM traffic per launch: ncu captures of the headline-size launches showed the inputs read exactly once
-        # (12.66 MB for the GEMM, 16.81 MB for the fused quantiser) and the outputs still in L2 at kernel end, so
+        # (12.67 MB for the GEMM, 16.81 MB for the fused quantiser) and the outputs still in L2 at kernel end, so
         # traffic = input bytes read + output bytes written back later; only reported for the captured size.
         headline = (m, k, n_local) == (2048, 4096, 4096)
-        gemm_traffic = 12.66e6 + 2.0 * m * n_local if headline else None
+        gemm_traffic = 12.67e6 + 2.0 * m * n_local if headline else None
         f1_traffic = 16.81e6 + m * k / 2 + 6.0 * m if headline else None
         if args.workload == "hadamard_quantize":
             value, unit, t_main = f1_bytes / t_f1 / 1e9, "GB/s", t_f1
@@ -368,11 +370,12 @@ def run_b200(args):
                        "parallelism": (f"N-sharded x{world}, " + ("epilogue pushes tiles to every GPU + barrier" if args.exchange == "push"
                                                                        else "NCCL all-gather + interleave copy")) if world > 1 else "single GPU",
                        "inputs": "activations Student-t(nu=4) unit RMS bf16; weights N(0,0.02) quantised to packed int4"},
-            "roofline": {"kernel": "gemm_i4_kernel (tcgen05 kind::i8, fused dequant epilogue)", "bound": "tensor",
+            "roofline": {"kernel": "gemm_i4_wide_kernel / gemm_i4_kernel (TMA -> int4 unpack -> tcgen05 kind::i8, fused dequant epilogue;"
+                                   " 256x256 tiles at the default shape)", "bound": "tensor",
                          "achieved": ops_gemm / t_gemm / 1e12 if t_gemm > 0 else None, "peak": int8_peak,
                          "unit": "TOPS", "frac": (ops_gemm / t_gemm / 1e12) / int8_peak if t_gemm > 0 else None,
                          "peak_source": f"2 x bf16_tflops ({peaks['bf16_tflops']}) of {peaks['source']}",
-                         "traffic": gemm_traffic, "traffic_note": "12.66 MB read measured by ncu on this launch size plus the output"
+                         "traffic": gemm_traffic, "traffic_note": "12.67 MB read measured by ncu on this launch size plus the output"
                                                                    " bytes, which L2 writes back after the kernel (profiles/)",
                          "us_per_launch": t_gemm * 1e6},
             "roofline_hadamard_quantize": {"kernel": "hadamard_quant_mma_kernel (fused Hadamard+scale+quantise+pack)", "bound": "hbm",

@@ -27,6 +27,9 @@ inline int launch_status() {
     return cuda_status(e);
 }
 
+// Reads and clears the device status word of the row-kernel translation unit (see tcgen05.cuh).
+int hq_tc_fetch_and_clear_device_status(int* out);
+
 // ---------------------------------------------------------------------------------------------
 // Device-side helpers
 // ---------------------------------------------------------------------------------------------

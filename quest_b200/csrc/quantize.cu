@@ -12,6 +12,7 @@
 //   two rounding points decide the codes - the Hadamard output is rounded to bf16 before anything
 //   else looks at it, and the scale is rounded to bf16 before the divide.
 #include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace qb {
 
@@ -743,6 +744,10 @@ static int launch_row(const RowParams& p, cudaStream_t stream) {
     return launch_status();
 }
 
+#include "hadamard_quant_tc.cuh"
+
+int hq_tc_fetch_and_clear_device_status(int* out) { return fetch_and_clear_device_status(out); }
+
 static bool vector_path_ok(const RowParams& p) {
     if (p.K % 8 != 0 || p.K > kMaxVectorK) return false;
     if (!aligned16(p.x)) return false;
@@ -899,6 +904,17 @@ extern "C" int hadamard_quantize_int4_cuda_bf16(void* x_int_packed_ptr, void* sc
     p.quantize = 1;
     p.had_scale = __bfloat162float(__float2bfloat16_rn((float)(1.0 / sqrt((double)block))));
     if (!vector_path_ok(p)) return QB200_ERR_UNSUPPORTED;
+    // Tensor-core kernel where the shape fits its tiling; QB200_HQ_KERNEL=mma|tc forces one (tests, tuning).
+    const char* force = getenv("QB200_HQ_KERNEL");
+    const bool want_tc = force != nullptr ? (force[0] == 't') : true;
+    if (want_tc && hq_tc_eligible(p, block)) {
+        switch (block) {
+            case 64: return launch_hq_tc<64>(p, stream);
+            case 128: return launch_hq_tc<128>(p, stream);
+            default: return launch_hq_tc<256>(p, stream);
+        }
+    }
+    if (force != nullptr && force[0] == 't') return QB200_ERR_UNSUPPORTED;
     switch (block) {
         case 64: return launch_hq_mma<64>(p, stream);
         case 128: return launch_hq_mma<128>(p, stream);

@@ -35,10 +35,10 @@ constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(128 
 }  // namespace tc
 
 // Block 256: index bit 7 pairs neighbouring rows of X2 (the two 128-element halves of a 256 block): lanes l, l ^ 1.
-__device__ __forceinline__ void pair_rows(uint32_t (&r)[32], int lane) {
+__device__ __forceinline__ void pair_rows(uint32_t (&r)[16], int lane) {
     const float sgn = (lane & 1) ? -1.f : 1.f;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
+    for (int i = 0; i < 16; ++i) {
         const float x = __uint_as_float(r[i]);
         const float o = __shfl_xor_sync(0xffffffffu, x, 1);
         r[i] = __float_as_uint(fmaf(x, sgn, o));  // even row: first half + second half; odd row: first - second
@@ -90,11 +90,18 @@ hadamard_quant_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const RowPa
         tmem_alloc(tmem_slot, 512);
         tmem_relinquish();
     }
-    // The Hadamard operand: H[o][k] = h * (-1)^popc(o & k), K-major rows of 128 bytes per K half, 128-byte swizzle
-    // (16-byte chunk index XOR (row & 7)), exactly the layout TMA gives the activation tile.
-    {
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_acc = *tmem_slot_ptr;
+    const int rows_per_tile = T * nb;
+
+    if (warp != 0) {
+        // The Hadamard operand, built while the producer warp already fetches the first tiles:
+        // H[o][k] = h * (-1)^popc(o & k), K-major rows of 128 bytes per K half, 128-byte swizzle (16-byte chunk
+        // index XOR (row & 7)), exactly the layout TMA gives the activation tile.
         const uint32_t hb = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(p.had_scale));
-        for (int item = threadIdx.x; item < 128 * 16; item += kThreads) {
+        for (int item = threadIdx.x - 32; item < 128 * 16; item += kThreads - 32) {
             const int o = item >> 4, ch = item & 15;  // row, 16-byte chunk of the 256-byte row
             const int half = ch >> 3, c = ch & 7;
             uint32_t w[4];
@@ -113,12 +120,8 @@ hadamard_quant_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const RowPa
             sts128(h_base + half * HALF_BYTES + o * 128 + ((c ^ (o & 7)) << 4), make_uint4(w[0], w[1], w[2], w[3]));
         }
         fence_proxy_async_smem();
+        asm volatile("bar.sync 1, %0;" ::"n"(kThreads - 32) : "memory");
     }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_acc = *tmem_slot_ptr;
-    const int rows_per_tile = T * nb;
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
@@ -197,19 +200,28 @@ hadamard_quant_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const RowPa
             tc_fence_after();
 
             // ---- pass 1: sum of squares of the bf16-rounded transform ----
+            // Tensor memory is read in pieces of 16 columns into two register sets: the next piece is in flight
+            // while the current one is processed.
+            uint32_t ra[16], rb[16];
             f32x2 ssq2 = 0ull;
-#pragma unroll 1
-            for (int c0 = 0; c0 < 128; c0 += 32) {
-                uint32_t r[32];
-                tmem_ld32(t_row + c0, r);
-                tmem_ld_wait();
+            auto square_sum = [&](uint32_t (&r)[16]) {
                 if (HB == 256) pair_rows(r, lane);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
+                for (int i = 0; i < 8; ++i) {
                     const uint32_t v = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
                     const f32x2 xx = pk2(bf16lo_to_f32(v), bf16hi_to_f32(v));
                     ssq2 = fma2(xx, xx, ssq2);
                 }
+            };
+            tmem_ld16(t_row, ra);
+#pragma unroll
+            for (int c = 0; c < 8; c += 2) {
+                tmem_ld_wait16(ra);
+                tmem_ld16(t_row + 16 * (c + 1), rb);
+                square_sum(ra);
+                tmem_ld_wait16(rb);
+                tmem_ld16(t_row + (c + 2 < 8 ? 16 * (c + 2) : 0), ra);  // last: the first piece of pass 2
+                square_sum(rb);
             }
             float ssq;
             {
@@ -240,18 +252,13 @@ hadamard_quant_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const RowPa
             const f32x2 inv_s2 = pk2(inv_s, inv_s), magic2 = pk2(kFloorMagic, kFloorMagic);
             if (valid && blk == 0) p.scale_out[token] = sb;
 
-            // ---- pass 2: quantise and pack; 32 consecutive elements = 16 packed bytes per piece ----
+            // ---- pass 2: quantise and pack; 16 consecutive elements = 8 packed bytes per piece ----
             uint8_t* const dst = p.q_packed + (size_t)token * (K >> 1) + blk * 64;
             int rs16 = 0;
-#pragma unroll 1
-            for (int c0 = 0; c0 < 128; c0 += 32) {
-                uint32_t r[32];
-                tmem_ld32(t_row + c0, r);
-                tmem_ld_wait();
+            auto quantise16 = [&](uint32_t (&r)[16], uint32_t& w0, uint32_t& w1) {
                 if (HB == 256) pair_rows(r, lane);
-                uint32_t w[4];
 #pragma unroll
-                for (int q8 = 0; q8 < 4; ++q8) {  // eight elements -> one 32-bit word
+                for (int q8 = 0; q8 < 2; ++q8) {  // eight elements -> one 32-bit word
                     uint32_t ub[8];
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
@@ -268,12 +275,23 @@ hadamard_quant_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const RowPa
                     // byte j of the word = (code[2j+1] << 4) | code[2j]
                     const uint32_t ev = __byte_perm(__byte_perm(ub[0], ub[2], 0x0040), __byte_perm(ub[4], ub[6], 0x0040), 0x5410);
                     const uint32_t od = __byte_perm(__byte_perm(ub[1], ub[3], 0x0040), __byte_perm(ub[5], ub[7], 0x0040), 0x5410);
-                    w[q8] = (ev & 0x0F0F0F0Fu) | ((od << 4) & 0xF0F0F0F0u);
+                    const uint32_t word = (ev & 0x0F0F0F0Fu) | ((od << 4) & 0xF0F0F0F0u);
+                    if (q8 == 0) w0 = word; else w1 = word;
                 }
+            };
+#pragma unroll
+            for (int c = 0; c < 8; c += 2) {
+                uint32_t w[4];
+                tmem_ld_wait16(ra);
+                tmem_ld16(t_row + 16 * (c + 1), rb);
+                quantise16(ra, w[0], w[1]);
+                tmem_ld_wait16(rb);
+                if (c + 2 < 8) tmem_ld16(t_row + 16 * (c + 2), ra);
+                quantise16(rb, w[2], w[3]);
                 if (valid) {
 #pragma unroll
                     for (int q8 = 0; q8 < 4; ++q8) rs16 = nibble_sum16(w[q8], rs16);
-                    *reinterpret_cast<uint4*>(dst + (c0 >> 1)) = make_uint4(w[0], w[1], w[2], w[3]);
+                    *reinterpret_cast<uint4*>(dst + 8 * c) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
             }
             // the accumulator buffer has been read for the last time
@@ -297,6 +315,7 @@ hadamard_quant_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const RowPa
             }
             if (valid && blk == 0 && p.row_sum != nullptr) p.row_sum[token] = rs16 >> 4;  // exact: every term is a multiple of 16
         }
+        tmem_ld_wait();  // a prefetched piece may still be in flight if a bounded wait gave up
     }
 
     tc_fence_before();

@@ -906,7 +906,9 @@ extern "C" int hadamard_quantize_int4_cuda_bf16(void* x_int_packed_ptr, void* sc
     if (!vector_path_ok(p)) return QB200_ERR_UNSUPPORTED;
     // Tensor-core kernel where the shape fits its tiling; QB200_HQ_KERNEL=mma|tc forces one (tests, tuning).
     const char* force = getenv("QB200_HQ_KERNEL");
-    const bool want_tc = force != nullptr ? (force[0] == 't') : true;
+    // Measured crossover: below ~12 M elements the launch is one short wave and the CUDA-core kernel's smaller
+    // set-up wins by about a microsecond.
+    const bool want_tc = force != nullptr ? (force[0] == 't') : ((long long)p.M * p.K >= 12ll * 1024 * 1024);
     if (want_tc && hq_tc_eligible(p, block)) {
         switch (block) {
             case 64: return launch_hq_tc<64>(p, stream);

@@ -137,10 +137,48 @@ def check_hadamard_quantize(x: torch.Tensor, block: int) -> tuple[int, int, int]
     return xh_mism, nflip, scale_flips
 
 
+# "tc": the tcgen05 kernel where the shape fits its tiling (it must: the call fails otherwise); "mma": the CUDA-core
+# kernel with mma.sync for the 16-point factor; "auto": what the library picks.
+HQ_TC_SHAPES = [("student", 128, 4096), ("laplace", 64, 8192), ("randn", 33, 14336), ("outlier", 7, 2048),
+                ("randn", 1, 256), ("student", 300, 512), ("laplace", 5, 16384), ("randn", 1000, 128)]
+
+
+@pytest.mark.parametrize("block", [64, 128, 256])
+@pytest.mark.parametrize("kind,m,k", HQ_TC_SHAPES)
+def test_hadamard_quantize_tensor_core_kernel_matches_oracle(block, kind, m, k, monkeypatch):
+    if k % block != 0:
+        pytest.skip("K is not a multiple of the block")
+    monkeypatch.setenv("QB200_HQ_KERNEL", "tc")
+    x = make_activations(kind, m, k, seed=block + m)
+    xh_mism, nflip, scale_flips = check_hadamard_quantize(x, block)
+    n = m * k
+    assert nflip <= 1 + int(5e-6 * n), (nflip, n)
+    assert scale_flips <= max(1, m // 1000)
+
+
+@pytest.mark.parametrize("block", [64, 128, 256])
+def test_hadamard_quantize_kernels_agree_at_full_size(block, monkeypatch):
+    """The two kernels on the headline activation shape: same scales, codes equal up to +-1 tie flips."""
+    x = make_activations("student", 2048, 4096, seed=9).to(DEV)
+    out = {}
+    for kern in ("mma", "tc"):
+        monkeypatch.setenv("QB200_HQ_KERNEL", kern)
+        out[kern] = [t.cpu() for t in quest.hadamard_quantize_int4(x, block)]
+    (p1, s1, r1), (p2, s2, r2) = out["mma"], out["tc"]
+    assert int((s1 != s2).sum()) <= 2
+    same = (s1 == s2).view(-1)
+    nflip, maxd = O.count_code_flips(p1[same], p2[same])
+    assert maxd <= 1 and nflip <= 1 + int(5e-6 * x.numel())
+    assert r2.equal(O.unpack_int4(p2).to(torch.int32).sum(-1, keepdim=True))
+
+
 @pytest.mark.parametrize("block", [64, 128, 256])
 @pytest.mark.parametrize("kind,m,k", [("student", 128, 4096), ("laplace", 64, 8192), ("randn", 33, 14336),
                                       ("outlier", 7, 2048), ("randn", 3, 28672), ("randn", 1, 256)])
-def test_hadamard_quantize_matches_oracle(block, kind, m, k):
+@pytest.mark.parametrize("kernel", ["auto", "mma"])
+def test_hadamard_quantize_matches_oracle(block, kind, m, k, kernel, monkeypatch):
+    if kernel != "auto":
+        monkeypatch.setenv("QB200_HQ_KERNEL", kernel)
     x = make_activations(kind, m, k, seed=block + m)
     xh_mism, nflip, scale_flips = check_hadamard_quantize(x, block)
     n = m * k

@@ -378,7 +378,8 @@ def run_b200(args):
                          "traffic": gemm_traffic, "traffic_note": "12.67 MB read measured by ncu on this launch size plus the output"
                                                                    " bytes, which L2 writes back after the kernel (profiles/)",
                          "us_per_launch": t_gemm * 1e6},
-            "roofline_hadamard_quantize": {"kernel": "hadamard_quant_mma_kernel (fused Hadamard+scale+quantise+pack)", "bound": "hbm",
+            "roofline_hadamard_quantize": {"kernel": "fused Hadamard+scale+quantise+pack: hadamard_quant_tc_kernel (tcgen05) from 12 M elements,"
+                                                     " hadamard_quant_mma_kernel below (the default shape)", "bound": "hbm",
                                            "achieved": f1_bytes / t_f1 / 1e9 if t_f1 > 0 else None,
                                            "peak": peaks["hbm_gbs"], "unit": "GB/s",
                                            "frac": (f1_bytes / t_f1 / 1e9) / peaks["hbm_gbs"] if t_f1 > 0 else None,

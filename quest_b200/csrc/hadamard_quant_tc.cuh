@@ -7,9 +7,9 @@
 //
 //   TMA (cp.async.bulk.tensor.2d, 128-byte swizzle)   128 rows of X2 (32 KB)  global -> shared      producer warp
 //   tcgen05.mma kind::f16, M128 N128 K16, 8 per tile  X2 tile . H -> 128 x 128 fp32 in tensor memory one thread
-//   tcgen05.ld 32x32b.x32                             thread = (row of X2, 32 of its 128 columns)    16 drain warps
-//   round to bf16 pairs (kept in registers), sum of squares, two-level reduction per token through shared memory,
-//   scale, saturate, divide-free floor, nibble pack, one 16-byte store per thread, row sums one tile later.
+//   tcgen05.ld / tcgen05.st 32x32b                    thread = one row of X2 (one 128-element block)  16 drain warps
+//   pass 1: round to bf16 pairs (written back into tensor memory), sum of squares, per-token reduction, scale;
+//   pass 2: saturate, divide-free floor, nibble pack, 16-byte stores, row sums.
 //
 // This is the same "x times Hadamard matrix" product the reference hands to cuBLAS (gemm-quest/benchmarks/utils.py:
 // 17, 89-90); it moves the butterflies off the instruction-issue-bound CUDA cores, which is what limits
@@ -204,25 +204,31 @@ hadamard_quant_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const RowPa
             // while the current one is processed.
             uint32_t ra[16], rb[16];
             f32x2 ssq2 = 0ull;
-            auto square_sum = [&](uint32_t (&r)[16]) {
+            // Each piece is rounded to bf16 pairs once; the pairs go back into the columns of the accumulator that
+            // have already been read (piece c -> columns 8c .. 8c+7), so pass 2 neither re-rounds nor re-pairs.
+            auto square_sum = [&](uint32_t (&r)[16], int c) {
                 if (HB == 256) pair_rows(r, lane);
+                uint32_t v[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    const uint32_t v = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-                    const f32x2 xx = pk2(bf16lo_to_f32(v), bf16hi_to_f32(v));
+                    v[i] = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+                    const f32x2 xx = pk2(bf16lo_to_f32(v[i]), bf16hi_to_f32(v[i]));
                     ssq2 = fma2(xx, xx, ssq2);
                 }
+                tmem_st8(t_row + 8 * c, v);
             };
             tmem_ld16(t_row, ra);
 #pragma unroll
             for (int c = 0; c < 8; c += 2) {
                 tmem_ld_wait16(ra);
                 tmem_ld16(t_row + 16 * (c + 1), rb);
-                square_sum(ra);
+                square_sum(ra, c);
                 tmem_ld_wait16(rb);
-                tmem_ld16(t_row + (c + 2 < 8 ? 16 * (c + 2) : 0), ra);  // last: the first piece of pass 2
-                square_sum(rb);
+                if (c + 2 < 8) tmem_ld16(t_row + 16 * (c + 2), ra);
+                square_sum(rb, c + 1);
             }
+            tmem_st_wait();
+            tmem_ld16(t_row, ra);  // the first 32 rounded values for pass 2, in flight during the scale computation
             float ssq;
             {
                 float s0, s1;
@@ -252,18 +258,17 @@ hadamard_quant_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const RowPa
             const f32x2 inv_s2 = pk2(inv_s, inv_s), magic2 = pk2(kFloorMagic, kFloorMagic);
             if (valid && blk == 0) p.scale_out[token] = sb;
 
-            // ---- pass 2: quantise and pack; 16 consecutive elements = 8 packed bytes per piece ----
+            // ---- pass 2: quantise and pack; a piece is 16 columns of bf16 pairs = 32 elements = 16 packed bytes ----
             uint8_t* const dst = p.q_packed + (size_t)token * (K >> 1) + blk * 64;
             int rs16 = 0;
-            auto quantise16 = [&](uint32_t (&r)[16], uint32_t& w0, uint32_t& w1) {
-                if (HB == 256) pair_rows(r, lane);
+            auto quantise32 = [&](const uint32_t (&v)[16], int piece) {
+                uint32_t w[4];
 #pragma unroll
-                for (int q8 = 0; q8 < 2; ++q8) {  // eight elements -> one 32-bit word
+                for (int q8 = 0; q8 < 4; ++q8) {  // eight elements -> one 32-bit word
                     uint32_t ub[8];
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        const uint32_t v = pack_bf16x2(__uint_as_float(r[8 * q8 + 2 * i]), __uint_as_float(r[8 * q8 + 2 * i + 1]));
-                        const uint32_t c = clamp_bf16x2(v, lo2, hi2);
+                        const uint32_t c = clamp_bf16x2(v[4 * q8 + i], lo2, hi2);
                         float y0, y1;
                         unpk2(mul2(pk2(bf16lo_to_f32(c), bf16hi_to_f32(c)), inv_s2), y0, y1);
                         const f32x2 fl = add2_rd(pk2(fmaf(fabsf(y0), 1.220703125e-4f, y0), fmaf(fabsf(y1), 1.220703125e-4f, y1)), magic2);
@@ -275,24 +280,22 @@ hadamard_quant_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const RowPa
                     // byte j of the word = (code[2j+1] << 4) | code[2j]
                     const uint32_t ev = __byte_perm(__byte_perm(ub[0], ub[2], 0x0040), __byte_perm(ub[4], ub[6], 0x0040), 0x5410);
                     const uint32_t od = __byte_perm(__byte_perm(ub[1], ub[3], 0x0040), __byte_perm(ub[5], ub[7], 0x0040), 0x5410);
-                    const uint32_t word = (ev & 0x0F0F0F0Fu) | ((od << 4) & 0xF0F0F0F0u);
-                    if (q8 == 0) w0 = word; else w1 = word;
+                    w[q8] = (ev & 0x0F0F0F0Fu) | ((od << 4) & 0xF0F0F0F0u);
                 }
-            };
-#pragma unroll
-            for (int c = 0; c < 8; c += 2) {
-                uint32_t w[4];
-                tmem_ld_wait16(ra);
-                tmem_ld16(t_row + 16 * (c + 1), rb);
-                quantise16(ra, w[0], w[1]);
-                tmem_ld_wait16(rb);
-                if (c + 2 < 8) tmem_ld16(t_row + 16 * (c + 2), ra);
-                quantise16(rb, w[2], w[3]);
                 if (valid) {
 #pragma unroll
                     for (int q8 = 0; q8 < 4; ++q8) rs16 = nibble_sum16(w[q8], rs16);
-                    *reinterpret_cast<uint4*>(dst + 8 * c) = make_uint4(w[0], w[1], w[2], w[3]);
+                    *reinterpret_cast<uint4*>(dst + 16 * piece) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
+            };
+#pragma unroll
+            for (int pc = 0; pc < 4; pc += 2) {
+                tmem_ld_wait16(ra);
+                tmem_ld16(t_row + 16 * (pc + 1), rb);
+                quantise32(ra, pc);
+                tmem_ld_wait16(rb);
+                if (pc + 2 < 4) tmem_ld16(t_row + 16 * (pc + 2), ra);
+                quantise32(rb, pc + 1);
             }
             // the accumulator buffer has been read for the last time
             tc_fence_before();

@@ -163,7 +163,10 @@ def run_reference(args):
         "steps": r["steps_timed"], "warmup": min(args.warmup, 2), "ms_per_step": r["seconds_per_step"] * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int4 codes, fp32 exact matmul (CPU)",
         "data": "synthetic",
-        "config": {"workload": f"W4A4 linear M={args.m} K={args.k} N={args.n} block={args.block} (CPU torch path)"},
+        "config": {"workload": f"linear: W4A4 linear M={args.m} K={args.k} N={args.n} per GPU"
+                               f" (N_total={args.n * args.gpus}), Hadamard block {args.block}",
+                   "sample": "one GPU's share of the layer (all M rows, N columns) per step, on the host cores",
+                   "inputs": "activations Student-t(nu=4) unit RMS bf16; weights N(0,0.02) quantised to packed int4"},
         "cpu_baseline": {"value": r["tops"], "unit": "TOPS", "cores": r["cores"], "kind": "port", "sample": r["sample"]},
         "e2e": {"value": r["tops"], "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,

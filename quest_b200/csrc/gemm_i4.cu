@@ -86,6 +86,10 @@ struct EpilogueParams {
     int vec_ok;             // 1: 16-byte stores are aligned for every (row, 16-byte column group); 2: 32-byte ones too
     int n_peer;             // fused only: the tile is also stored into n_peer further matrices of the same shape
     void* peer_out[7];      // (buffers of other GPUs mapped into this address space: plain peer stores)
+    // split-K (few output tiles, long K): every tile is computed by `splits` CTAs over disjoint K ranges
+    int splits;             // 1 = off
+    int32_t* scratch;       // [tile * splits + range][128 rows][256 columns] int32 partial sums
+    int* counters;          // one per output tile, all zero between launches
 };
 
 
@@ -176,7 +180,10 @@ __device__ __forceinline__ void unpack_x16(const uint4& pk, uint4& lo, uint4& hi
 // ---------------------------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------------------------
-template <int BN, bool FUSED>
+// SPLIT: a work item is (output tile, K range).  The epilogue adds its shifted int32 partial sums into ep.scratch with
+// integer atomics (exact, order-independent); the CTA that completes a tile (a counter per tile tells) reads the
+// sums back, applies the normal epilogue and leaves scratch and counter zeroed for the next launch.
+template <int BN, bool FUSED, bool SPLIT = false>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_i4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const EpilogueParams ep, const int M, const int N, const int K) {
@@ -207,6 +214,12 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const int tiles_n = (N + BN - 1) / BN;
     const int num_tiles = tiles_m * tiles_n;
     const int num_kb = (K + BK - 1) / BK;
+    // work items: output tiles, or (tile, K range) pairs with split-K
+    const int S = SPLIT ? ep.splits : 1;
+    const int num_items = num_tiles * S;
+    auto tile_of = [&](int item) { return SPLIT ? item / S : item; };
+    auto kb_first = [&](int item) { return SPLIT ? (int)((long long)(item % S) * num_kb / S) : 0; };
+    auto kb_last = [&](int item) { return SPLIT ? (int)((long long)(item % S + 1) * num_kb / S) : num_kb; };
 
     if (threadIdx.x == 0) {
         QB_TRACE(0);
@@ -245,10 +258,11 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             tma_prefetch_desc(&tmap_b);
             uint32_t it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+                const int tile = tile_of(item);
                 const int m0 = (tile % tiles_m) * BM;
                 const int n0 = (tile / tiles_m) * BN;
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                for (int kb = kb_first(item), kb1 = kb_last(item); kb < kb1; ++kb, ++it) {
                     const uint32_t s = it % C::P_STAGES, ph = (it / C::P_STAGES) & 1u;
                     if (!(ok = mbar_wait(empty_p + 8 * s, ph ^ 1u, 1))) break;
                     mbar_arrive_expect_tx(full_p + 8 * s, C::P_BYTES);
@@ -269,12 +283,13 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (lane == 0) {
             uint32_t it = 0, local_tile = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+            for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x, ++local_tile) {
                 const uint32_t acc = local_tile & 1u, acc_ph = (local_tile >> 1) & 1u;
                 if (!(ok = mbar_wait(tmem_empty + 8 * acc, acc_ph ^ 1u, 3))) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_acc + acc * BN;
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const int kb0 = kb_first(item);
+                for (int kb = kb0, kb1 = kb_last(item); kb < kb1; ++kb, ++it) {
                     const uint32_t s = it % C::U_STAGES, ph = (it / C::U_STAGES) & 1u;
                     if (!(ok = mbar_wait(full_u + 8 * s, ph, 4))) break;
                     tc_fence_after();
@@ -284,7 +299,7 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 #pragma unroll
                     for (int j = 0; j < BK / 32; ++j) {
                         umma_i8(d_tmem, make_smem_desc(a_addr + 32 * j), make_smem_desc(b_addr + 32 * j), C::IDESC,
-                                (kb | j) != 0 ? 1u : 0u);
+                                (kb != kb0 || j != 0) ? 1u : 0u);
                     }
                     umma_commit(empty_u + 8 * s);  // frees the int8 stage once these MMAs have read it
                 }
@@ -302,7 +317,8 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         uint8_t* vec_ptr = smem_raw + (vec_base - smem_u32(smem_raw));
         uint32_t local_tile = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+        for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x, ++local_tile) {
+            const int tile = tile_of(item);
             const int m0 = (tile % tiles_m) * BM;
             const int n0 = (tile / tiles_m) * BN;
             const uint32_t acc = local_tile & 1u, acc_ph = (local_tile >> 1) & 1u;
@@ -331,8 +347,95 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             if (!ok) break;
             tc_fence_after();
             const uint32_t t_row = tmem_acc + ((uint32_t)(quad * 32) << 16) + acc * BN;
+            if (SPLIT) {
+                // This K range's partial sums -> the work item's own slab of scratch, [row of the tile][column],
+                // plain 32-byte stores (rows inside M only).  No atomics, and nothing has to be zeroed.
+                const int rows_valid = min(BM, M - m0);
+                int32_t* slab = ep.scratch + (size_t)item * (BM * BN);
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 64) {
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    if (n0 + c0 >= N) break;  // warp-uniform
+                    uint32_t r0[32];
+                    tmem_ld32(t_row + c0, r0);
+                    tmem_ld_wait();
+                    if (row_ok) {
+                        int32_t* dst = slab + (quad * 32 + lane) * BN + c0;
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            uint32_t w[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) w[i] = (uint32_t)((int)r0[8 * g + i] >> 8);
+                            stg256(dst + 8 * g, w);
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tmem_empty + 8 * acc);
+                // which CTA completes the tile?  The one whose increment of the tile's counter finds splits - 1.
+                __threadfence();
+                asm volatile("bar.sync 1, %0;" ::"n"(kNumEpilogueWarps * 32) : "memory");
+                int* flag = reinterpret_cast<int*>(smem_raw + (tmem_slot + 8 - smem_u32(smem_raw)));
+                if (et == 0) *flag = (atomicAdd(ep.counters + tile, 1) == S - 1) ? 1 : 0;
+                asm volatile("bar.sync 1, %0;" ::"n"(kNumEpilogueWarps * 32) : "memory");
+                if (*flag) {
+                    // Sum the S slabs of the tile and apply the epilogue.  The (row, 8-column group) pieces are dealt
+                    // out over all 128 epilogue threads, so that few valid rows still mean many loads in flight.
+                    __threadfence();
+                    const int32_t* tile_slabs = ep.scratch + (size_t)tile * S * (BM * BN);
+                    const int groups = BN / 8;
+                    for (int piece = et; piece < rows_valid * groups; piece += kNumEpilogueWarps * 32) {
+                        const int pr = piece / groups, pc = (piece - pr * groups) * 8;
+                        if (n0 + pc >= N) continue;
+                        int acc8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                        const int4* src = reinterpret_cast<const int4*>(tile_slabs + pr * BN + pc);
+                        constexpr int kSlabInt4 = BM * BN / 4;
+                        for (int sp = 0; sp < S; sp += 4) {  // four slabs' loads are in flight before the first add
+                            int4 v[4][2];
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) {
+                                const bool in = sp + u < S;
+                                v[u][0] = in ? __ldcg(src + (size_t)(sp + u) * kSlabInt4) : make_int4(0, 0, 0, 0);
+                                v[u][1] = in ? __ldcg(src + (size_t)(sp + u) * kSlabInt4 + 1) : make_int4(0, 0, 0, 0);
+                            }
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) {
+                                acc8[0] += v[u][0].x; acc8[1] += v[u][0].y; acc8[2] += v[u][0].z; acc8[3] += v[u][0].w;
+                                acc8[4] += v[u][1].x; acc8[5] += v[u][1].y; acc8[6] += v[u][1].z; acc8[7] += v[u][1].w;
+                            }
+                        }
+                        const int prow = m0 + pr;
+                        if (FUSED) {
+                            const int pa = ep.a_add[prow];
+                            const float pm = 0.5f * bf16_to_f32(ep.a_mul[prow]);
+                            __nv_bfloat16* out = static_cast<__nv_bfloat16*>(ep.out) + (size_t)prow * ep.ld + n0 + pc;
+                            uint32_t w[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const float v0 = (float)(2 * acc8[2 * i] + pa + sb_add[pc + 2 * i]) * (pm * sb_mul[pc + 2 * i]);
+                                const float v1 = (float)(2 * acc8[2 * i + 1] + pa + sb_add[pc + 2 * i + 1]) * (pm * sb_mul[pc + 2 * i + 1]);
+                                w[i] = pack_bf16x2(v0, v1);
+                            }
+                            if (ep.vec_ok && n0 + pc + 8 <= N) {
+                                *reinterpret_cast<uint4*>(out) = make_uint4(w[0], w[1], w[2], w[3]);
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 8; ++i)
+                                    if (n0 + pc + i < N) reinterpret_cast<uint16_t*>(out)[i] = (uint16_t)(w[i / 2] >> (16 * (i & 1)));
+                            }
+                        } else {
+                            int32_t* out = static_cast<int32_t*>(ep.out) + (size_t)prow * ep.ld + n0 + pc;
+#pragma unroll
+                            for (int i = 0; i < 8; ++i)
+                                if (n0 + pc + i < N) out[i] = acc8[i];
+                        }
+                    }
+                    if (et == 0) ep.counters[tile] = 0;  // ready for the next launch
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(kNumEpilogueWarps * 32) : "memory");  // the flag is reused by the next item
+            }
+#pragma unroll 1
+            for (int c0 = 0; !SPLIT && c0 < BN; c0 += 64) {
                 if (n0 + c0 >= N) break;  // warp-uniform
                 uint32_t r0[32], r1[32];
                 tmem_ld32(t_row + c0, r0);
@@ -343,12 +446,13 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 if (n0 + c0 + 32 < N)
                     epilogue_store_chunk<FUSED>(r1, ep, row, n0 + c0 + 32, N, a_add, half_a_mul, sb_add + c0 + 32, sb_mul + c0 + 32);
             }
-            // This warp has finished reading the accumulator buffer.
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(tmem_empty + 8 * acc);
+            if (!SPLIT) {  // this warp has finished reading the accumulator buffer
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tmem_empty + 8 * acc);
+            }
             if (warp == kFirstEpilogueWarp && lane == 0) QB_TRACE(3);
-            if (FUSED && ep.n_peer > 0) {
+            if (!SPLIT && FUSED && ep.n_peer > 0) {
                 // Hand the tile (now in the local output) to the push warps; at most two tiles may be pending.
                 ok = mbar_wait(push_free + 8 * acc, acc_ph ^ 1u, 11);
                 ok = __all_sync(0xffffffffu, ok);
@@ -367,7 +471,8 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const int pw = warp - kFirstPushWarp;
             uint32_t local_tile = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+            for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x, ++local_tile) {
+                const int tile = tile_of(item);
                 const int m0 = (tile % tiles_m) * BM;
                 const int n0 = (tile / tiles_m) * BN;
                 const uint32_t acc = local_tile & 1u, acc_ph = (local_tile >> 1) & 1u;
@@ -405,8 +510,8 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const int t = threadIdx.x - kFirstUnpackWarp * 32;  // 0 .. 255
         uint32_t it = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-            for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+            for (int kb = kb_first(item), kb1 = kb_last(item); kb < kb1; ++kb, ++it) {
                 const uint32_t ps = it % C::P_STAGES, pph = (it / C::P_STAGES) & 1u;
                 const uint32_t us = it % C::U_STAGES, uph = (it / C::U_STAGES) & 1u;
                 ok = mbar_wait(full_p + 8 * ps, pph, 7) && mbar_wait(empty_u + 8 * us, uph ^ 1u, 8);
@@ -786,12 +891,12 @@ static int sm_count_of_current_device(int* dev_out) {
     return cached[dev];
 }
 
-template <int BN, bool FUSED>
+template <int BN, bool FUSED, bool SPLIT = false>
 static int launch_gemm(const EpilogueParams& ep, const void* a, const void* b, int M, int K, int N, int sms, int dev,
                        cudaStream_t stream) {
     using C = Cfg<BN>;
     static bool attr_set[64] = {false};
-    auto kernel = gemm_i4_kernel<BN, FUSED>;
+    auto kernel = gemm_i4_kernel<BN, FUSED, SPLIT>;
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
             return QB200_ERR_CUDA;
@@ -802,12 +907,71 @@ static int launch_gemm(const EpilogueParams& ep, const void* a, const void* b, i
     if (st != QB200_OK) return st;
     st = make_packed_map(&mb, b, N, K, BN);
     if (st != QB200_OK) return st;
-    const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-    const int grid = tiles < sms ? tiles : sms;
+    const int items = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * (SPLIT ? ep.splits : 1);
+    const int grid = items < sms ? items : sms;
     kernel<<<grid, kNumThreads, C::SMEM_BYTES, stream>>>(ma, mb, ep, M, N, K);
     return launch_status();
 }
 
+// ---- split-K scratch --------------------------------------------------------------------------------------------
+// Split-K needs a 128 x 256 int32 slab per work item (tile, K range) and one counter per output tile; the counters are
+// zero between launches (the kernel leaves them so), the slabs need no initialisation.  The ordinary entry points keep one such buffer per device, allocated (and zeroed) on first use and grown on
+// demand - never while the stream is being captured into a graph, where the launch falls back to the kernel without
+// split-K.  One split-K launch per device may be in flight at a time (launches on one stream are).
+struct SplitScratch {
+    int32_t* sums = nullptr;
+    int* counters = nullptr;
+    size_t ints = 0;
+    int tiles = 0;
+};
+static SplitScratch g_split_scratch[64];
+static std::mutex g_split_mutex;
+
+static bool get_split_scratch(int dev, cudaStream_t stream, size_t need_ints, int need_tiles, SplitScratch* out) {
+    if (dev < 0 || dev >= 64) return false;
+    std::lock_guard<std::mutex> lock(g_split_mutex);
+    SplitScratch& ws = g_split_scratch[dev];
+    if (ws.ints < need_ints || ws.tiles < need_tiles) {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+            cudaGetLastError();
+            return false;
+        }
+        if (cudaDeviceSynchronize() != cudaSuccess) return false;  // nothing may still use the old buffer
+        if (ws.sums) cudaFree(ws.sums);
+        ws = SplitScratch{};
+        const size_t ints = need_ints > (size_t)4 << 20 ? need_ints : (size_t)4 << 20;
+        const int tiles = need_tiles > 1024 ? need_tiles : 1024;
+        void* ptr = nullptr;
+        if (cudaMalloc(&ptr, (ints + (size_t)tiles) * sizeof(int)) != cudaSuccess) {
+            cudaGetLastError();
+            return false;
+        }
+        if (cudaMemset(ptr, 0, (ints + (size_t)tiles) * sizeof(int)) != cudaSuccess) {
+            cudaFree(ptr);
+            cudaGetLastError();
+            return false;
+        }
+        ws.sums = static_cast<int32_t*>(ptr);
+        ws.counters = reinterpret_cast<int*>(ws.sums + ints);
+        ws.ints = ints;
+        ws.tiles = tiles;
+    }
+    *out = ws;
+    return true;
+}
+
+// Number of K ranges for the 128 x 256 kernel, or 1.  Split-K pays when the output has so few tiles that most SMs
+// would idle while each busy one walks the whole K serially (small M: the MMA issue rate, ~154 cycles per K=32 step
+// whatever the tile width, makes a CTA need ~10 us for K = 4096).
+static int pick_splits(int M, int N, int K, int sms) {
+    const long long tiles = (long long)((M + BM - 1) / BM) * ((N + 255) / 256);
+    const int num_kb = (K + BK - 1) / BK;
+    long long s = sms / tiles;
+    if (s > num_kb / 2) s = num_kb / 2;
+    if (s > 16) s = 16;
+    return s >= 2 ? (int)s : 1;
+}
 
 template <bool FUSED>
 static int launch_gemm_wide(const EpilogueParams& ep, const void* a, const void* b, int M, int K, int N, int sms, int dev,
@@ -833,7 +997,7 @@ static int launch_gemm_wide(const EpilogueParams& ep, const void* a, const void*
 // Tile shapes: 64, 128, 256 = gemm_i4_kernel<BN> (128-row tiles); kWideTile = gemm_i4_wide_kernel (256 x 256).
 constexpr int kWideTile = 512;
 
-static int pick_tile(int M, int N, int K, int sms) {
+static int pick_tile(int M, int N, int K, int sms, long long* est_cycles) {
     // Estimated cycles.  Per 128-K stage a CTA of the 128-row kernel needs about max(616, 3 * (128 + BN)) cycles:
     // the four MMAs take ~616 cycles whatever N is, the unpack moves 3 shared-memory wavefronts per operand row.
     // Wide tiles amortise the A rows; narrow ones fill more SMs when there are few tiles (small M).  The 256 x 256
@@ -841,7 +1005,10 @@ static int pick_tile(int M, int N, int K, int sms) {
     // QB200_GEMM_TILE = 64 | 128 | 256 | 512 in the environment forces a shape (tests and tuning).
     if (const char* e = getenv("QB200_GEMM_TILE")) {
         const int v = atoi(e);
-        if (v == 64 || v == 128 || v == 256 || v == kWideTile) return v;
+        if (v == 64 || v == 128 || v == 256 || v == kWideTile) {
+            *est_cycles = 0;  // forced: no split-K either
+            return v;
+        }
     }
     const long long kb = (K + BK - 1) / BK;
     int best = 256;
@@ -859,6 +1026,7 @@ static int pick_tile(int M, int N, int K, int sms) {
         const long long t = waves * (kb * 1536 + 7000);
         if (t < best_t) { best_t = t; best = kWideTile; }
     }
+    *est_cycles = best_t;
     return best;
 }
 
@@ -882,7 +1050,40 @@ static int run_gemm(bool fused, const EpilogueParams& ep_in, const void* a, cons
     int dev = 0;
     const int sms = sm_count_of_current_device(&dev);
     if (sms <= 0) return QB200_ERR_CUDA;
-    const int bn = pick_tile(M, N, K, sms);
+    long long est = 0;
+    const int bn = pick_tile(M, N, K, sms, &est);
+    // Split-K (128 x 256 tiles over several K ranges) when that is estimated to be faster and its scratch is there.
+    // QB200_GEMM_SPLITS = n in the environment forces n ranges (1 = never split).
+    int splits = 1;
+    if (ep.n_peer == 0) {
+        const int smax = pick_splits(M, N, K, sms);
+        if (const char* e = getenv("QB200_GEMM_SPLITS")) {
+            const int v = atoi(e);
+            const int num_kb = (K + BK - 1) / BK;
+            splits = v < 1 ? 1 : (v > num_kb ? num_kb : (v > 64 ? 64 : v));
+        } else if (smax >= 2 && est > 0) {
+            // K stages of the 128 x 256 kernel at ~1152 cycles, plus the completing CTA's reduction: it reads
+            // rows x splits KB through 128 threads (~40 cycles per row and range, measured), plus fixed costs.
+            const long long num_kb = (K + BK - 1) / BK;
+            const long long rows = M < BM ? M : BM;
+            long long best = est;
+            for (int sp = 2; sp <= smax; ++sp) {
+                const long long t = ((num_kb + sp - 1) / sp) * 1152 + rows * sp * 40 + 24 * 256 + 3000;
+                if (t < best) { best = t; splits = sp; }
+            }
+        }
+    }
+    if (splits >= 2) {
+        const int tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);
+        SplitScratch ws;
+        if (get_split_scratch(dev, stream, (size_t)tiles * splits * 256 * BM, tiles, &ws)) {
+            ep.splits = splits;
+            ep.scratch = ws.sums;
+            ep.counters = ws.counters;
+            return fused ? launch_gemm<256, true, true>(ep, a, b, M, K, N, sms, dev, stream)
+                         : launch_gemm<256, false, true>(ep, a, b, M, K, N, sms, dev, stream);
+        }
+    }
     if (bn == kWideTile)
         return fused ? launch_gemm_wide<true>(ep, a, b, M, K, N, sms, dev, stream)
                      : launch_gemm_wide<false>(ep, a, b, M, K, N, sms, dev, stream);

@@ -319,6 +319,33 @@ def test_wide_tile_kernel_full_size_against_cublas(monkeypatch):
     assert c.equal(ref)
 
 
+@pytest.mark.parametrize("splits", [2, 3, 8])
+@pytest.mark.parametrize("m,k,n", [(1, 4096, 512), (16, 1024, 264), (128, 2048, 1024), (130, 512, 300)])
+def test_split_k_is_bit_exact_and_leaves_its_scratch_clean(splits, m, k, n, monkeypatch):
+    """QB200_GEMM_SPLITS forces the split-K kernel; two calls in a row must both be exact (the second one sees the
+    scratch the first one left behind), for the int32 and the fused entry points."""
+    monkeypatch.setenv("QB200_GEMM_SPLITS", str(splits))
+    a, b = random_packed(m, k, 61), random_packed(n, k, 62)
+    ad, bd = a.to(DEV), b.to(DEV)
+    a_add, a_mul, b_add, b_mul = epilogue_inputs(m, n, 63)
+    ref_i = O.matmul_int4_int4t_int32(a, b)
+    ref_f = O.fused_matmul_dequantize_int4_int4t_bf16(a, b, a_add, b_add, a_mul, b_mul)
+    for _ in range(2):
+        assert quest.matmul_int4_int4t_int32(ad, bd).cpu().equal(ref_i)
+        got = quest.fused_matmul_dequantize_int4_int4t_bf16(ad, bd, a_add.to(DEV), b_add.to(DEV), a_mul.to(DEV), b_mul.to(DEV))
+        assert got.cpu().equal(ref_f)
+
+
+def test_small_m_gemm_picks_split_k_and_matches_cublas():
+    """Decode-like shape (M=16, K=N=4096): whatever the library picks must equal cuBLAS int8 on the unpacked codes."""
+    m, k, n = 16, 4096, 4096
+    ad, bd = random_packed(m, k, 71).to(DEV), random_packed(n, k, 72).to(DEV)
+    ref = torch._int_mm(torch.cat([quest.unpack_int4(ad), torch.zeros(16, k, dtype=torch.int8, device=DEV)]),
+                        quest.unpack_int4(bd).t().contiguous())[:m]
+    for _ in range(3):
+        assert quest.matmul_int4_int4t_int32(ad, bd).equal(ref)
+
+
 def test_fused_into_column_slice():
     m, k, n, n_total = 96, 512, 128, 512
     a, b = random_packed(m, k, 31), random_packed(n, k, 32)

@@ -88,7 +88,8 @@ struct EpilogueParams {
     void* peer_out[7];      // (buffers of other GPUs mapped into this address space: plain peer stores)
     // split-K (few output tiles, long K): every tile is computed by `splits` CTAs over disjoint K ranges
     int splits;             // 1 = off
-    int32_t* scratch;       // [tile * splits + range][128 rows][256 columns] int32 partial sums
+    int32_t* scratch;       // [tile * splits + range][slab_rows][256 columns] int32 partial sums
+    int slab_ints;          // slab_rows * 256: a slab holds only the rows a tile can have (M rounded up to 8, at most 128)
     int* counters;          // one per output tile, all zero between launches
 };
 
@@ -351,7 +352,7 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 // This K range's partial sums -> the work item's own slab of scratch, [row of the tile][column],
                 // plain 32-byte stores (rows inside M only).  No atomics, and nothing has to be zeroed.
                 const int rows_valid = min(BM, M - m0);
-                int32_t* slab = ep.scratch + (size_t)item * (BM * BN);
+                int32_t* slab = ep.scratch + (size_t)item * ep.slab_ints;
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN; c0 += 32) {
                     if (n0 + c0 >= N) break;  // warp-uniform
@@ -382,14 +383,14 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     // Sum the S slabs of the tile and apply the epilogue.  The (row, 8-column group) pieces are dealt
                     // out over all 128 epilogue threads, so that few valid rows still mean many loads in flight.
                     __threadfence();
-                    const int32_t* tile_slabs = ep.scratch + (size_t)tile * S * (BM * BN);
+                    const int32_t* tile_slabs = ep.scratch + (size_t)tile * S * ep.slab_ints;
                     const int groups = BN / 8;
                     for (int piece = et; piece < rows_valid * groups; piece += kNumEpilogueWarps * 32) {
                         const int pr = piece / groups, pc = (piece - pr * groups) * 8;
                         if (n0 + pc >= N) continue;
                         int acc8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
                         const int4* src = reinterpret_cast<const int4*>(tile_slabs + pr * BN + pc);
-                        constexpr int kSlabInt4 = BM * BN / 4;
+                        const int kSlabInt4 = ep.slab_ints / 4;
                         for (int sp = 0; sp < S; sp += 4) {  // four slabs' loads are in flight before the first add
                             int4 v[4][2];
 #pragma unroll
@@ -914,7 +915,7 @@ static int launch_gemm(const EpilogueParams& ep, const void* a, const void* b, i
 }
 
 // ---- split-K scratch --------------------------------------------------------------------------------------------
-// Split-K needs a 128 x 256 int32 slab per work item (tile, K range) and one counter per output tile; the counters are
+// Split-K needs a rows x 256 int32 slab per work item (tile, K range) and one counter per output tile; the counters are
 // zero between launches (the kernel leaves them so), the slabs need no initialisation.  The ordinary entry points keep one such buffer per device, allocated (and zeroed) on first use and grown on
 // demand - never while the stream is being captured into a graph, where the launch falls back to the kernel without
 // split-K.  One split-K launch per device may be in flight at a time (launches on one stream are).
@@ -940,7 +941,7 @@ static bool get_split_scratch(int dev, cudaStream_t stream, size_t need_ints, in
         if (cudaDeviceSynchronize() != cudaSuccess) return false;  // nothing may still use the old buffer
         if (ws.sums) cudaFree(ws.sums);
         ws = SplitScratch{};
-        const size_t ints = need_ints > (size_t)4 << 20 ? need_ints : (size_t)4 << 20;
+        const size_t ints = need_ints > (size_t)2 << 20 ? need_ints : (size_t)2 << 20;
         const int tiles = need_tiles > 1024 ? need_tiles : 1024;
         void* ptr = nullptr;
         if (cudaMalloc(&ptr, (ints + (size_t)tiles) * sizeof(int)) != cudaSuccess) {
@@ -1075,8 +1076,10 @@ static int run_gemm(bool fused, const EpilogueParams& ep_in, const void* a, cons
     }
     if (splits >= 2) {
         const int tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);
+        const int slab_rows = M >= BM ? BM : (M + 7) / 8 * 8;
+        ep.slab_ints = slab_rows * 256;
         SplitScratch ws;
-        if (get_split_scratch(dev, stream, (size_t)tiles * splits * 256 * BM, tiles, &ws)) {
+        if (get_split_scratch(dev, stream, (size_t)tiles * splits * ep.slab_ints, tiles, &ws)) {
             ep.splits = splits;
             ep.scratch = ws.sums;
             ep.counters = ws.counters;

@@ -33,7 +33,8 @@ enum {
     QB200_ERR_UNSUPPORTED = 2,      /* shape outside what the kernels cover (see each function) */
     QB200_ERR_CUDA = 3,             /* a CUDA runtime call or kernel launch failed */
     QB200_ERR_DRIVER = 4,           /* cuTensorMapEncodeTiled unavailable or failed */
-    QB200_ERR_DEVICE_TIMEOUT = 5    /* a bounded in-kernel wait gave up (reported by quest_b200_device_status) */
+    QB200_ERR_DEVICE_TIMEOUT = 5,   /* a bounded in-kernel wait gave up (reported by quest_b200_device_status) */
+    QB200_ERR_SCRATCH_LIMIT = 6     /* the no-allocation entry point was asked for more scratch than its static buffer */
 };
 
 /* Human-readable text for a status code. */
@@ -119,6 +120,20 @@ int fused_matmul_dequantize_int4_int4t_bf16_strided_cuda(void* mat_d, long long 
                                                          const void* vec_b_add, const void* vec_a_mul,
                                                          const void* vec_b_mul, int M, int K, int N,
                                                          cudaStream_t stream);
+
+/*
+ * The fused GEMM + epilogue for callers that must not trigger any allocation (graph capture, allocator-controlled
+ * processes): when it runs the split-K kernel its scratch is a fixed 8 MiB array in device memory (static storage of
+ * the library, address taken once per device) instead of the per-device buffer the other entry points allocate on
+ * first use.  splits = 0 lets the library choose the number of K ranges (1 = the kernels without scratch), splits
+ * >= 2 asks for that many.  Returns QB200_ERR_SCRATCH_LIMIT, and launches nothing, if
+ * tiles x splits x rows-per-tile exceeds 8192 (tiles = ceil(M/128) * ceil(N/256), rows-per-tile = min(128, M rounded
+ * up to 8)).  One such launch per device may be in flight at a time.  No counterpart in the reference.
+ */
+int fused_matmul_dequantize_int4_int4t_bf16_noalloc_cuda(void* mat_d, const void* mat_a, const void* mat_b,
+                                                         const void* vec_a_add, const void* vec_b_add,
+                                                         const void* vec_a_mul, const void* vec_b_mul, int M, int K,
+                                                         int N, int splits, cudaStream_t stream);
 
 /*
  * Same GEMM + epilogue, with every output tile stored into n_dst (1..8) matrices of identical shape and row

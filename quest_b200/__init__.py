@@ -67,6 +67,29 @@ def fused_matmul_dequantize_int4_int4t_bf16_into(
     return out_cols
 
 
+def fused_matmul_dequantize_int4_int4t_bf16_noalloc(
+        mat_a: torch.Tensor,
+        mat_b: torch.Tensor,
+        vec_a_add: torch.Tensor,
+        vec_b_add: torch.Tensor,
+        vec_a_mul: torch.Tensor,
+        vec_b_mul: torch.Tensor,
+        out: torch.Tensor,
+        splits: int = 0,
+) -> torch.Tensor:
+    """Same computation through the entry point that allocates nothing: ``out`` is required, and a split-K launch
+    takes its scratch from the library's fixed 8 MiB device array (``splits`` = 0: the library's choice of K ranges,
+    n >= 2: n ranges).  Raises if the scratch needed exceeds that array."""
+    assert mat_a.dtype == torch.uint8 and mat_b.dtype == torch.uint8 and vec_a_add.dtype == torch.int32 and vec_b_add.dtype == torch.int32 and vec_a_mul.dtype == torch.bfloat16 and vec_b_mul.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    assert mat_a.is_contiguous() and mat_b.is_contiguous() and vec_a_add.is_contiguous() and vec_b_add.is_contiguous() and vec_a_mul.is_contiguous() and vec_b_mul.is_contiguous() and out.is_contiguous()
+    assert out.shape == (mat_a.size(0), mat_b.size(0))
+    dev = _lib.require_cuda(mat_a, mat_b, vec_a_add, vec_b_add, vec_a_mul, vec_b_mul, out)
+    _call("fused_matmul_dequantize_int4_int4t_bf16_noalloc_cuda", dev, _lib.ptr(out), _lib.ptr(mat_a), _lib.ptr(mat_b),
+          _lib.ptr(vec_a_add), _lib.ptr(vec_b_add), _lib.ptr(vec_a_mul), _lib.ptr(vec_b_mul), mat_a.size(0),
+          mat_b.size(1) * 2, mat_b.size(0), int(splits), _lib.stream_of(mat_a))
+    return out
+
+
 def fused_matmul_dequantize_int4_int4t_bf16_push(
         mat_a: torch.Tensor,
         mat_b: torch.Tensor,

@@ -21,6 +21,7 @@ SIGNATURES = {
     "add_mul_vv_cuda_bf16": [_P, _P, _P, _P, _P, _P, _I, _I, _P],
     "matmul_int4_int4t_int32_cuda": [_P, _P, _P, _I, _I, _I, _P],
     "fused_matmul_dequantize_int4_int4t_bf16_cuda": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
+    "fused_matmul_dequantize_int4_int4t_bf16_noalloc_cuda": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
     "fused_matmul_dequantize_int4_int4t_bf16_strided_cuda": [_P, _LL, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     "fused_matmul_dequantize_int4_int4t_bf16_push_cuda": [ctypes.POINTER(ctypes.c_void_p), _I, _LL, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     "hadamard_quantize_int4_cuda_bf16": [_P, _P, _P, _P, _I, _I, _I, _P],

@@ -962,6 +962,32 @@ static bool get_split_scratch(int dev, cudaStream_t stream, size_t need_ints, in
     return true;
 }
 
+// The same scratch as a fixed array in device memory, for the entry point that must not allocate: 2 Mi int32
+// (8 MiB) of slabs - work items x rows per slab <= 8192 - and 1024 tile counters.  Static storage is zero at module
+// load and the kernel leaves the counters zero, so nothing ever has to initialise it.
+constexpr size_t kStaticScratchInts = (size_t)2 << 20;
+constexpr int kStaticScratchTiles = 1024;
+static __device__ __align__(256) int g_static_scratch[kStaticScratchInts + kStaticScratchTiles];
+
+static bool get_static_scratch(int dev, SplitScratch* out) {
+    static int32_t* cached[64] = {nullptr};  // the symbol's address, looked up once per device
+    if (dev < 0 || dev >= 64) return false;
+    std::lock_guard<std::mutex> lock(g_split_mutex);
+    if (cached[dev] == nullptr) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || ptr == nullptr) {
+            cudaGetLastError();
+            return false;
+        }
+        cached[dev] = static_cast<int32_t*>(ptr);
+    }
+    out->sums = cached[dev];
+    out->counters = reinterpret_cast<int*>(cached[dev] + kStaticScratchInts);
+    out->ints = kStaticScratchInts;
+    out->tiles = kStaticScratchTiles;
+    return true;
+}
+
 // Number of K ranges for the 128 x 256 kernel, or 1.  Split-K pays when the output has so few tiles that most SMs
 // would idle while each busy one walks the whole K serially (small M: the MMA issue rate, ~154 cycles per K=32 step
 // whatever the tile width, makes a CTA need ~10 us for K = 4096).
@@ -1031,8 +1057,10 @@ static int pick_tile(int M, int N, int K, int sms, long long* est_cycles) {
     return best;
 }
 
+// static_splits < 0: the ordinary entry points (split-K scratch from the per-device buffer).  static_splits >= 0: the
+// entry point that allocates nothing (scratch in the static array; 0 = the library's choice of K ranges, n = n ranges).
 static int run_gemm(bool fused, const EpilogueParams& ep_in, const void* a, const void* b, int M, int K, int N,
-                    cudaStream_t stream) {
+                    cudaStream_t stream, int static_splits = -1) {
     if (M < 0 || N < 0 || K < 0) return QB200_ERR_INVALID_ARGUMENT;
     if (M == 0 || N == 0) return QB200_OK;
     if (ep_in.out == nullptr || a == nullptr || b == nullptr) return QB200_ERR_INVALID_ARGUMENT;
@@ -1074,12 +1102,25 @@ static int run_gemm(bool fused, const EpilogueParams& ep_in, const void* a, cons
             }
         }
     }
+    if (static_splits > 0) {
+        const int num_kb = (K + BK - 1) / BK;
+        splits = static_splits > num_kb ? num_kb : static_splits;
+    }
     if (splits >= 2) {
         const int tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);
         const int slab_rows = M >= BM ? BM : (M + 7) / 8 * 8;
         ep.slab_ints = slab_rows * 256;
+        const size_t need = (size_t)tiles * splits * ep.slab_ints;
         SplitScratch ws;
-        if (get_split_scratch(dev, stream, (size_t)tiles * splits * ep.slab_ints, tiles, &ws)) {
+        bool have;
+        if (static_splits >= 0) {
+            if (need > kStaticScratchInts || tiles > kStaticScratchTiles) return QB200_ERR_SCRATCH_LIMIT;
+            have = get_static_scratch(dev, &ws);
+            if (!have) return QB200_ERR_CUDA;
+        } else {
+            have = get_split_scratch(dev, stream, need, tiles, &ws);
+        }
+        if (have) {
             ep.splits = splits;
             ep.scratch = ws.sums;
             ep.counters = ws.counters;
@@ -1149,6 +1190,22 @@ extern "C" int fused_matmul_dequantize_int4_int4t_bf16_push_cuda(void* const* ma
     return run_gemm(true, ep, mat_a, mat_b, M, K, N, stream);
 }
 
+extern "C" int fused_matmul_dequantize_int4_int4t_bf16_noalloc_cuda(void* mat_d, const void* mat_a, const void* mat_b,
+                                                                    const void* vec_a_add, const void* vec_b_add,
+                                                                    const void* vec_a_mul, const void* vec_b_mul, int M,
+                                                                    int K, int N, int splits, cudaStream_t stream) {
+    if (M > 0 && N > 0 && (!vec_a_add || !vec_b_add || !vec_a_mul || !vec_b_mul)) return QB200_ERR_INVALID_ARGUMENT;
+    if (splits < 0) return QB200_ERR_INVALID_ARGUMENT;
+    EpilogueParams ep{};
+    ep.out = mat_d;
+    ep.ld = N;
+    ep.a_add = static_cast<const int32_t*>(vec_a_add);
+    ep.b_add = static_cast<const int32_t*>(vec_b_add);
+    ep.a_mul = static_cast<const __nv_bfloat16*>(vec_a_mul);
+    ep.b_mul = static_cast<const __nv_bfloat16*>(vec_b_mul);
+    return run_gemm(true, ep, mat_a, mat_b, M, K, N, stream, splits);
+}
+
 extern "C" int fused_matmul_dequantize_int4_int4t_bf16_cuda(void* mat_d, const void* mat_a, const void* mat_b,
                                                             const void* vec_a_add, const void* vec_b_add,
                                                             const void* vec_a_mul, const void* vec_b_mul, int M, int K,
@@ -1177,6 +1234,8 @@ extern "C" const char* quest_b200_error_string(int status) {
         case QB200_ERR_CUDA: return "CUDA runtime call or kernel launch failed";
         case QB200_ERR_DRIVER: return "cuTensorMapEncodeTiled unavailable or failed";
         case QB200_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel timed out";
+        case QB200_ERR_SCRATCH_LIMIT:
+            return "split-K scratch would exceed the 8 MiB static buffer (tiles x splits x rows per tile must be <= 8192)";
         default: return "unknown status";
     }
 }

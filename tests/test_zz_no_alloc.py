@@ -1,0 +1,68 @@
+"""GPU test of the entry point that allocates nothing (fused_matmul_dequantize_int4_int4t_bf16_noalloc_cuda): its
+split-K scratch is a fixed array in device memory.  Collected last (file name) so that the per-device scratch buffer of
+the ordinary entry point already exists when the two are compared."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+from oracle import quest_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+if torch.cuda.is_available():
+    import quest_b200 as quest
+    DEV = torch.device("cuda:0")
+
+
+def _inputs(m, k, n, seed):
+    g = torch.Generator().manual_seed(seed)
+    a = O.pack_int4(torch.randint(-8, 8, (m, k), generator=g, dtype=torch.int8))
+    b = O.pack_int4(torch.randint(-8, 8, (n, k), generator=g, dtype=torch.int8))
+    a_add = torch.randint(-512, 512, (m, 1), generator=g, dtype=torch.int32)
+    b_add = torch.randint(-512, 512, (n, 1), generator=g, dtype=torch.int32)
+    a_mul = (torch.rand(m, 1, generator=g) + 0.05).to(torch.bfloat16)
+    b_mul = (0.02 * torch.rand(n, 1, generator=g) + 0.001).to(torch.bfloat16)
+    return a, b, a_add, b_add, a_mul, b_mul
+
+
+@pytest.mark.parametrize("m,k,n,splits", [(16, 4096, 4096, 0), (1, 2048, 1024, 4), (40, 1024, 520, 3), (128, 512, 256, 2),
+                                          (300, 512, 264, 0)])
+def test_noalloc_entry_point_matches_the_ordinary_one_twice(m, k, n, splits):
+    host = _inputs(m, k, n, seed=m + n)
+    a, b, a_add, b_add, a_mul, b_mul = (t.to(DEV) for t in host)
+    ref = O.fused_matmul_dequantize_int4_int4t_bf16(host[0], host[1], host[2], host[3], host[4], host[5])
+    out = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    for _ in range(2):  # the second call finds the scratch as the first one left it
+        ordinary = quest.fused_matmul_dequantize_int4_int4t_bf16(a, b, a_add, b_add, a_mul, b_mul)
+        out.fill_(float("nan"))
+        ret = quest.fused_matmul_dequantize_int4_int4t_bf16_noalloc(a, b, a_add, b_add, a_mul, b_mul, out, splits=splits)
+        assert ret is out
+        assert out.equal(ordinary)
+        assert out.cpu().equal(ref)
+    assert quest.device_status() == 0
+
+
+def test_noalloc_entry_point_does_not_allocate_device_memory():
+    a, b, a_add, b_add, a_mul, b_mul = (t.to(DEV) for t in _inputs(16, 4096, 4096, seed=5))
+    out = torch.empty(16, 4096, dtype=torch.bfloat16, device=DEV)
+    quest.fused_matmul_dequantize_int4_int4t_bf16_noalloc(a, b, a_add, b_add, a_mul, b_mul, out, splits=8)
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        quest.fused_matmul_dequantize_int4_int4t_bf16_noalloc(a, b, a_add, b_add, a_mul, b_mul, out, splits=8)
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0
+
+
+def test_noalloc_entry_point_rejects_scratch_beyond_its_static_buffer():
+    m, k, n = 128, 4096, 8192  # 32 tiles x 8 ranges x 128 rows = 32768 > 8192
+    a, b, a_add, b_add, a_mul, b_mul = (t.to(DEV) for t in _inputs(m, k, n, seed=6))
+    out = torch.zeros(m, n, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(RuntimeError, match="static buffer"):
+        quest.fused_matmul_dequantize_int4_int4t_bf16_noalloc(a, b, a_add, b_add, a_mul, b_mul, out, splits=8)
+    assert float(out.abs().max()) == 0.0  # nothing was launched
+    # the same shape with the library's own choice needs no scratch and runs
+    quest.fused_matmul_dequantize_int4_int4t_bf16_noalloc(a, b, a_add, b_add, a_mul, b_mul, out, splits=0)
+    assert out.equal(quest.fused_matmul_dequantize_int4_int4t_bf16(a, b, a_add, b_add, a_mul, b_mul))

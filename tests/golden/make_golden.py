@@ -85,7 +85,9 @@ def make_case(fn: dict, name: str, activation: torch.Tensor, weight: torch.Tenso
 
 
 def main() -> None:
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("QUEST_REFERENCE_ROOT")
+    if not ref_root:
+        sys.exit("usage: make_golden.py <path of the reference checkout>  (or set QUEST_REFERENCE_ROOT)")
     fn = load_reference_functions(ref_root)
 
     g = torch.Generator().manual_seed(0)

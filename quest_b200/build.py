@@ -17,7 +17,7 @@ ROOT = os.path.dirname(PKG_DIR)
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libquest_b200.so")
 SOURCES = ("quantize.cu", "gemm_i4.cu")
-HEADERS = (os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "tcgen05.cuh"), os.path.join(CSRC, "hadamard_quant_tc.cuh"),
+HEADERS = (os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "tcgen05.cuh"), os.path.join(CSRC, "hadamard_quant_tc.cuh"), os.path.join(CSRC, "gemv_i4.cuh"),
            os.path.join(ROOT, "include", "quest_b200.h"))
 
 NVCC_FLAGS = [

@@ -1021,6 +1021,8 @@ static int launch_gemm_wide(const EpilogueParams& ep, const void* a, const void*
     return launch_status();
 }
 
+#include "gemv_i4.cuh"
+
 // Tile shapes: 64, 128, 256 = gemm_i4_kernel<BN> (128-row tiles); kWideTile = gemm_i4_wide_kernel (256 x 256).
 constexpr int kWideTile = 512;
 
@@ -1079,6 +1081,15 @@ static int run_gemm(bool fused, const EpilogueParams& ep_in, const void* a, cons
     int dev = 0;
     const int sms = sm_count_of_current_device(&dev);
     if (sms <= 0) return QB200_ERR_CUDA;
+    // Up to 16 rows: the CUDA-core kernel that streams the weights once (QB200_GEMM_GEMV=0 switches it off; a forced
+    // tile shape or split count also means the tensor-core kernels are wanted).
+    {
+        const char* g = getenv("QB200_GEMM_GEMV");
+        const bool forced_tc = getenv("QB200_GEMM_TILE") != nullptr || getenv("QB200_GEMM_SPLITS") != nullptr;
+        if (static_splits <= 0 && !forced_tc && !(g != nullptr && g[0] == '0') && gemv_eligible(M, K, N, ep.n_peer))
+            return fused ? run_gemv<true>(ep, a, b, M, K, N, sms, dev, stream)
+                         : run_gemv<false>(ep, a, b, M, K, N, sms, dev, stream);
+    }
     long long est = 0;
     const int bn = pick_tile(M, N, K, sms, &est);
     // Split-K (128 x 256 tiles over several K ranges) when that is estimated to be faster and its scratch is there.

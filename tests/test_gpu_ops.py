@@ -346,6 +346,34 @@ def test_small_m_gemm_picks_split_k_and_matches_cublas():
         assert quest.matmul_int4_int4t_int32(ad, bd).equal(ref)
 
 
+@pytest.mark.parametrize("m", [1, 2, 3, 5, 8, 9, 16])
+@pytest.mark.parametrize("k,n", [(4096, 520), (256, 7), (14336, 260), (1024, 4104)])
+def test_small_m_cuda_core_kernel_is_bit_exact(m, k, n):
+    """M <= 16 with a small enough product takes the dp4a kernel: int32 and fused outputs against the oracle, twice."""
+    a, b = random_packed(m, k, 81), random_packed(n, k, 82)
+    ad, bd = a.to(DEV), b.to(DEV)
+    a_add, a_mul, b_add, b_mul = epilogue_inputs(m, n, 83)
+    ref_i = O.matmul_int4_int4t_int32(a, b)
+    ref_f = O.fused_matmul_dequantize_int4_int4t_bf16(a, b, a_add, b_add, a_mul, b_mul)
+    for _ in range(2):
+        assert quest.matmul_int4_int4t_int32(ad, bd).cpu().equal(ref_i)
+        got = quest.fused_matmul_dequantize_int4_int4t_bf16(ad, bd, a_add.to(DEV), b_add.to(DEV), a_mul.to(DEV), b_mul.to(DEV))
+        assert got.cpu().equal(ref_f)
+
+
+def test_small_m_kernels_agree_on_extreme_codes(monkeypatch):
+    """All codes -8 at the longest K: the dp4a kernel, the split-K kernel and the plain tensor-core kernel."""
+    m, k, n = 4, 28672, 136
+    a = torch.full((m, k // 2), 0x88, dtype=torch.uint8, device=DEV)
+    b = torch.full((n, k // 2), 0x88, dtype=torch.uint8, device=DEV)
+    c0 = quest.matmul_int4_int4t_int32(a, b)
+    assert int(c0.min()) == 64 * k and int(c0.max()) == 64 * k
+    monkeypatch.setenv("QB200_GEMM_GEMV", "0")
+    assert quest.matmul_int4_int4t_int32(a, b).equal(c0)
+    monkeypatch.setenv("QB200_GEMM_SPLITS", "1")
+    assert quest.matmul_int4_int4t_int32(a, b).equal(c0)
+
+
 def test_fused_into_column_slice():
     m, k, n, n_total = 96, 512, 128, 512
     a, b = random_packed(m, k, 31), random_packed(n, k, 32)

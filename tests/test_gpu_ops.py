@@ -529,3 +529,57 @@ def test_push_entry_point_copies_tiles_to_every_destination():
     for t in bufs:
         assert t[:, col0:col0 + n].cpu().equal(want)
         assert int(t[:, :col0].abs().sum()) == 0 and int(t[:, col0 + n:].abs().sum()) == 0
+
+
+# ------------------------------------------------------------------ checkpoint conversion -------------
+def test_checkpoint_conversion_matches_oracle_and_module_swap():
+    """A synthetic QuEST-style checkpoint (DDP-prefixed keys, block names of the reference's Llama model): every
+    quantised linear is packed exactly as the oracle's preprocess_weight does, the rest passes through, and a
+    model loaded from the converted entries computes what a model swapped in place computes."""
+    from quest_b200 import convert
+    g = torch.Generator().manual_seed(3)
+    d, ff = 256, 512
+
+    class Block(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.attn = torch.nn.Module()
+            self.attn.c_attn = torch.nn.Linear(d, 3 * d, bias=False)
+            self.attn.c_proj = torch.nn.Linear(d, d, bias=False)
+            self.mlp = torch.nn.Module()
+            self.mlp.w1 = torch.nn.Linear(d, ff, bias=False)
+            self.mlp.w2 = torch.nn.Linear(d, ff, bias=False)
+            self.mlp.c_proj = torch.nn.Linear(ff, d, bias=True)
+
+    class Tiny(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.transformer = torch.nn.ModuleDict({"wte": torch.nn.Embedding(64, d), "h": torch.nn.ModuleList([Block(), Block()])})
+            self.lm_head = torch.nn.Linear(d, 64, bias=False)
+
+    src = Tiny()
+    for p_ in src.parameters():
+        p_.data.copy_(0.05 * torch.randn(p_.shape, generator=g))
+    ckpt = {"model": {"module." + k: v for k, v in src.state_dict().items()}, "itr": 7}
+    sd = convert.unwrap_checkpoint(ckpt)
+    names = convert.quantised_layer_names(sd)
+    assert len(names) == 10 and "transformer.h.1.mlp.c_proj" in names and "lm_head" not in names
+    conv = convert.convert_state_dict(ckpt, device=DEV)
+    assert "transformer.h.0.attn.c_attn.weight" not in conv and conv["lm_head.weight"].dtype == torch.bfloat16
+    for name in names:
+        w = sd[name + ".weight"].to(torch.bfloat16)
+        p_ref, s_ref, a_ref, _ = O.preprocess_weight(w, use_hadamard=True)
+        assert conv[name + ".w_scale"].cpu().equal(s_ref)
+        nflip, maxd = O.count_code_flips(conv[name + ".w_int_packed"].cpu(), p_ref)
+        assert maxd <= 1 and nflip <= 1 + int(5e-6 * w.numel())
+    # a model swapped in place vs a model filled from the converted entries
+    a = Tiny().to(DEV).to(torch.bfloat16)
+    a.load_state_dict({k: v.to(torch.bfloat16) for k, v in sd.items()})
+    convert.swap_quantised_linears(a, names)
+    b = Tiny().to(DEV).to(torch.bfloat16)
+    convert.swap_quantised_linears(b, names)   # same structure, its own (random) weights
+    convert.load_converted(b, conv)
+    x = torch.randn(5, d, generator=g).to(torch.bfloat16).to(DEV)
+    for blk_a, blk_b in zip(a.transformer["h"], b.transformer["h"]):
+        assert blk_a.mlp.c_proj(blk_a.mlp.w1(x)).equal(blk_b.mlp.c_proj(blk_b.mlp.w1(x)))
+        assert blk_a.attn.c_attn(x).equal(blk_b.attn.c_attn(x))

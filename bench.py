@@ -188,8 +188,8 @@ def run_b200(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        # NCCL prints its version banner on stdout at NCCL_DEBUG=VERSION/INFO; stdout carries the one JSON line
-        os.environ["NCCL_DEBUG"] = os.environ.get("QB200_NCCL_DEBUG", "WARN")
+        # NCCL writes its version banner and debug output to stdout; stdout carries the one JSON line
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=dev)
     peaks = measured_peaks()
 

@@ -587,10 +587,37 @@ static_assert(LAYOUT_BYTES <= SMEM_BYTES, "layout does not fit");
 constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }  // namespace wide
 
-template <bool FUSED>
-__global__ void __launch_bounds__(wide::kThreads, 1)
+// Copies this warp's share of a finished tile (rows part*8 .. +7, then every parts*8 further) from the local output
+// to the same place of every peer buffer: eight rows are loaded (L2) before the first 512-byte row segment is stored.
+__device__ __noinline__ void push_tile_rows(const EpilogueParams& ep, int m0, int n0, int rows, int cols, int part,
+                                            int parts, int lane) {
+    for (int r0 = part * 8; r0 < rows; r0 += parts * 8) {
+        for (int c = lane * 8; c < cols; c += 256) {
+            uint4 v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (r0 + j < rows) {
+                    const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(ep.out) + (size_t)(m0 + r0 + j) * ep.ld + n0 + c;
+                    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(v[j].x), "=r"(v[j].y), "=r"(v[j].z), "=r"(v[j].w) : "l"(src));
+                }
+            }
+            for (int pi = 0; pi < ep.n_peer; ++pi) {
+                __nv_bfloat16* dstp = static_cast<__nv_bfloat16*>(ep.peer_out[pi]) + (size_t)(m0 + r0) * ep.ld + n0 + c;
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (r0 + j < rows) *reinterpret_cast<uint4*>(dstp + (size_t)j * ep.ld) = v[j];
+            }
+        }
+    }
+}
+
+// PUSH: the multi-GPU variant (two more warps that copy finished tiles to the peers, helped by the epilogue warps on
+// a CTA's last tile); the single-GPU instantiation carries none of that code and is launched without those warps.
+template <bool FUSED, bool PUSH>
+__global__ void __launch_bounds__(PUSH ? wide::kThreads : wide::kThreads - 32 * wide::kPushWarps, 1)
 gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                    const EpilogueParams ep, const int M, const int N, const int K) {
+                    const __grid_constant__ EpilogueParams ep, const int M, const int N, const int K) {
     using namespace wide;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_base = smem_u32(smem_raw);
@@ -762,18 +789,25 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             __syncwarp();
             if (lane == 0) mbar_arrive(tmem_empty);
             if (warp == kFirstEpi && lane == 0) QB_TRACE(3);
-            if (FUSED && ep.n_peer > 0) {
+            if (PUSH) {
                 ok = mbar_wait(push_free + 8 * slot, slot_ph ^ 1u, 11);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 __threadfence_block();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(out_ready + 8 * slot);
+                if (tile + (int)gridDim.x >= num_tiles) {  // last tile: wait until all of it is in the local output, then help
+                    ok = mbar_wait(out_ready + 8 * slot, slot_ph, 18);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    push_tile_rows(ep, m0, n0, min(TM, M - m0), min(TN, N - n0), kPushWarps + (warp - kFirstEpi),
+                                   kPushWarps + kEpiWarps, lane);
+                }
             }
         }
     } else if (warp >= kFirstPush) {
         // ------------------------------ push warps (multi-GPU only) ------------------------------
-        if (FUSED && ep.n_peer > 0) {
+        if (PUSH) {
             const int pw = warp - kFirstPush;
             uint32_t local_tile = 0;
             bool ok = true;
@@ -786,25 +820,9 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 if (!ok) break;
                 const int rows = min(TM, M - m0);
                 const int cols = min(TN, N - n0);
-                for (int r0 = pw * 8; r0 < rows; r0 += kPushWarps * 8) {
-                    for (int c = lane * 8; c < cols; c += 256) {
-                        uint4 v[8];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            if (r0 + j < rows) {
-                                const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(ep.out) + (size_t)(m0 + r0 + j) * ep.ld + n0 + c;
-                                asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];"
-                                             : "=r"(v[j].x), "=r"(v[j].y), "=r"(v[j].z), "=r"(v[j].w) : "l"(src));
-                            }
-                        }
-                        for (int pi = 0; pi < ep.n_peer; ++pi) {
-                            __nv_bfloat16* dstp = static_cast<__nv_bfloat16*>(ep.peer_out[pi]) + (size_t)(m0 + r0) * ep.ld + n0 + c;
-#pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                if (r0 + j < rows) *reinterpret_cast<uint4*>(dstp + (size_t)j * ep.ld) = v[j];
-                        }
-                    }
-                }
+                // the CTA's last tile: the epilogue warps have nothing left to do and push as well
+                const bool last = tile + (int)gridDim.x >= num_tiles;
+                push_tile_rows(ep, m0, n0, rows, cols, pw, last ? kPushWarps + kEpiWarps : kPushWarps, lane);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(push_free + 8 * slot);
             }
@@ -910,7 +928,9 @@ static int launch_gemm(const EpilogueParams& ep, const void* a, const void* b, i
     if (st != QB200_OK) return st;
     const int items = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * (SPLIT ? ep.splits : 1);
     const int grid = items < sms ? items : sms;
-    kernel<<<grid, kNumThreads, C::SMEM_BYTES, stream>>>(ma, mb, ep, M, N, K);
+    // the two push warps are the last ones of the block: without peers they are simply not launched
+    const int threads = ep.n_peer > 0 ? kNumThreads : kNumThreads - 32 * kNumPushWarps;
+    kernel<<<grid, threads, C::SMEM_BYTES, stream>>>(ma, mb, ep, M, N, K);
     return launch_status();
 }
 
@@ -1000,11 +1020,11 @@ static int pick_splits(int M, int N, int K, int sms) {
     return s >= 2 ? (int)s : 1;
 }
 
-template <bool FUSED>
-static int launch_gemm_wide(const EpilogueParams& ep, const void* a, const void* b, int M, int K, int N, int sms, int dev,
-                            cudaStream_t stream) {
+template <bool FUSED, bool PUSH>
+static int launch_gemm_wide_impl(const EpilogueParams& ep, const void* a, const void* b, int M, int K, int N, int sms,
+                                 int dev, cudaStream_t stream) {
     static bool attr_set[64] = {false};
-    auto kernel = gemm_i4_wide_kernel<FUSED>;
+    auto kernel = gemm_i4_wide_kernel<FUSED, PUSH>;
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, wide::SMEM_BYTES) != cudaSuccess)
             return QB200_ERR_CUDA;
@@ -1017,8 +1037,16 @@ static int launch_gemm_wide(const EpilogueParams& ep, const void* a, const void*
     if (st != QB200_OK) return st;
     const int tiles = ((M + wide::TM - 1) / wide::TM) * ((N + wide::TN - 1) / wide::TN);
     const int grid = tiles < sms ? tiles : sms;
-    kernel<<<grid, wide::kThreads, wide::SMEM_BYTES, stream>>>(ma, mb, ep, M, N, K);
+    const int threads = PUSH ? wide::kThreads : wide::kThreads - 32 * wide::kPushWarps;
+    kernel<<<grid, threads, wide::SMEM_BYTES, stream>>>(ma, mb, ep, M, N, K);
     return launch_status();
+}
+
+template <bool FUSED>
+static int launch_gemm_wide(const EpilogueParams& ep, const void* a, const void* b, int M, int K, int N, int sms, int dev,
+                            cudaStream_t stream) {
+    if (FUSED && ep.n_peer > 0) return launch_gemm_wide_impl<FUSED, FUSED>(ep, a, b, M, K, N, sms, dev, stream);
+    return launch_gemm_wide_impl<FUSED, false>(ep, a, b, M, K, N, sms, dev, stream);
 }
 
 #include "gemv_i4.cuh"

@@ -72,6 +72,13 @@ hadamard_quant_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const RowPa
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+#ifdef QB200_TRACE
+    if (threadIdx.x == 0) {
+        const unsigned long long t = hq_gtime();
+        atomicMin(&g_hq_trace[0], t);
+        atomicMax(&g_hq_trace[1], t);
+    }
+#endif
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < STAGES; ++i) {
@@ -198,6 +205,13 @@ hadamard_quant_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const RowPa
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
+#ifdef QB200_TRACE
+            if (jt == 0 && grp == 0 && quad == 0 && lane == 0) {
+                const unsigned long long t = hq_gtime();
+                atomicMin(&g_hq_trace[4], t);
+                atomicMax(&g_hq_trace[5], t);
+            }
+#endif
 
             // ---- pass 1: sum of squares of the bf16-rounded transform ----
             // Tensor memory is read in pieces of 16 columns into two register sets: the next piece is in flight
@@ -323,6 +337,13 @@ hadamard_quant_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const RowPa
 
     tc_fence_before();
     __syncthreads();
+#ifdef QB200_TRACE
+    if (threadIdx.x == 0) {
+        const unsigned long long t = hq_gtime();
+        atomicMin(&g_hq_trace[2], t);
+        atomicMax(&g_hq_trace[3], t);
+    }
+#endif
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_acc, 512);

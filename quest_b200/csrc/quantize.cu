@@ -315,7 +315,7 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a
 // sums; the final row sums are written one batch later by warp 0.
 #ifdef QB200_TRACE
 // Tuning builds only: earliest block start, latest start, earliest end and latest end (globaltimer, ns) of the last launch.
-__device__ unsigned long long g_hq_trace[4] = {~0ull, 0ull, ~0ull, 0ull};
+__device__ unsigned long long g_hq_trace[6] = {~0ull, 0ull, ~0ull, 0ull, ~0ull, 0ull};  // [4], [5]: first accumulator ready (tcgen05 kernel)
 __device__ __forceinline__ unsigned long long hq_gtime() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -841,8 +841,8 @@ using namespace qb;
 #ifdef QB200_TRACE
 extern "C" int quest_b200_hq_trace(unsigned long long* out) {
     if (cudaDeviceSynchronize() != cudaSuccess) return QB200_ERR_CUDA;
-    if (cudaMemcpyFromSymbol(out, g_hq_trace, sizeof(unsigned long long) * 4) != cudaSuccess) return QB200_ERR_CUDA;
-    const unsigned long long init[4] = {~0ull, 0ull, ~0ull, 0ull};
+    if (cudaMemcpyFromSymbol(out, g_hq_trace, sizeof(unsigned long long) * 6) != cudaSuccess) return QB200_ERR_CUDA;
+    const unsigned long long init[6] = {~0ull, 0ull, ~0ull, 0ull, ~0ull, 0ull};
     return cuda_status(cudaMemcpyToSymbol(g_hq_trace, init, sizeof(init)));
 }
 #endif

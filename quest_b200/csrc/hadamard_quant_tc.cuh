@@ -13,8 +13,9 @@
 //
 // This is the same "x times Hadamard matrix" product the reference hands to cuBLAS (gemm-quest/benchmarks/utils.py:
 // 17, 89-90); it moves the butterflies off the instruction-issue-bound CUDA cores, which is what limits
-// hadamard_quant_mma_kernel.  A tile holds T whole tokens (T * K/128 <= 128 rows; leftover lanes idle), so every
-// per-token reduction stays inside one tile.  Every mbarrier wait is bounded (see mbar_wait).
+// hadamard_quant_mma_kernel.  A tile holds T whole tokens (T * K/128 <= 128 rows; leftover lanes idle) or, for
+// K > 16384, one half or quarter of a token; every per-token reduction stays inside one CTA.  Every mbarrier wait is
+// bounded (see mbar_wait).
 #pragma once
 
 #include "tcgen05.cuh"
@@ -45,11 +46,13 @@ __device__ __forceinline__ void pair_rows(uint32_t (&r)[16], int lane) {
     }
 }
 
-// nb: 128-element blocks per token (K / 128); T: tokens per tile.
+// nb: 128-element blocks per token (K / 128).  A unit is what a reduction needs together: T whole tokens in one tile
+// (P = 1, T * nb <= 128 rows), or one token spread over P = 2 or 4 consecutive tiles of nb / P rows (K > 16384), which
+// P neighbouring drain groups then process side by side.
 template <int HB>
 __global__ void __launch_bounds__(tc::kThreads, 1)
 hadamard_quant_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const RowParams p, const int nb, const int T,
-                         const int num_tiles) {
+                         const int P, const int num_units) {
     using namespace tc;
     extern __shared__ uint8_t tc_smem_raw[];
     const uint32_t raw_base = smem_u32(tc_smem_raw);
@@ -88,7 +91,7 @@ hadamard_quant_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const RowPa
         for (int i = 0; i < NUM_ACC; ++i) {
             mbar_init(tmem_full + 8 * i, 1);
             mbar_init(tmem_empty + 8 * i, 4);
-            mbar_init(part_bar + 8 * i, 4);
+            mbar_init(part_bar + 8 * i, 4 * P);  // the warps of the P groups that share a token
         }
         mbar_init(mma_done, 1);
         fence_barrier_init();
@@ -101,7 +104,8 @@ hadamard_quant_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const RowPa
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_acc = *tmem_slot_ptr;
-    const int rows_per_tile = T * nb;
+    const int rows_per_tile = P == 1 ? T * nb : nb / P;
+    const int unit_rows = P == 1 ? T * nb : nb;  // rows of X2 per unit
 
     if (warp != 0) {
         // The Hadamard operand, built while the producer warp already fetches the first tiles:
@@ -136,12 +140,14 @@ hadamard_quant_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const RowPa
             tma_prefetch_desc(&tmap_x);
             uint32_t it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+            for (;; ++it) {  // tile `it` of this CTA: part it % P of unit blockIdx.x + (it / P) * gridDim.x
+                const int unit = blockIdx.x + (int)(it / P) * gridDim.x;
+                if (unit >= num_units) break;
                 const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
                 if (!(ok = mbar_wait(empty + 8 * s, ph ^ 1u, 21))) break;
                 mbar_arrive_expect_tx(full + 8 * s, TILE_BYTES);
                 const uint32_t dst = a_base + s * TILE_BYTES;
-                const int row0 = tile * rows_per_tile;
+                const int row0 = unit * unit_rows + (int)(it % P) * rows_per_tile;
                 tma_load_2d(dst, &tmap_x, 0, row0, full + 8 * s);
                 tma_load_2d(dst + HALF_BYTES, &tmap_x, 64, row0, full + 8 * s);
             }
@@ -156,7 +162,8 @@ hadamard_quant_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const RowPa
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+            for (;; ++it) {
+                if (blockIdx.x + (int)(it / P) * gridDim.x >= num_units) break;
                 const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
                 const uint32_t acc = it % NUM_ACC, acc_ph = (it / NUM_ACC) & 1u;
                 if (!(ok = mbar_wait(tmem_empty + 8 * acc, acc_ph ^ 1u, 23))) break;
@@ -187,19 +194,25 @@ hadamard_quant_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const RowPa
         const int grp = (warp - kFirstDrain) >> 2;    // drain group = accumulator buffer
         const int row = quad * 32 + lane;             // row of the tile = lane of tensor memory
         const int g_rows = nb < 32 ? nb : 32;         // rows of one token inside this warp (a power of two, or all 32)
-        const int tok_in_tile = row / nb;
-        const int blk = row - tok_in_tile * nb;       // which block of its token this row is
-        const bool row_in_tile = row < T * nb;
+        const int part = grp % P;                     // which tile of its token this group processes (0 if P == 1)
+        const int set0 = grp - part;                  // first group of the set that shares a token
+        const int tok_in_tile = P == 1 ? row / nb : 0;
+        const int blk = P == 1 ? row - tok_in_tile * nb : part * rows_per_tile + row;  // which block of its token this row is
+        const bool row_in_tile = row < rows_per_tile;
         const bool cross = nb > 32;                   // a token spans several warps: exchange through shared memory
         const int K = p.K;
-        float* const xf = part_f + grp * 8;           // [2][4]: per quadrant partial sums of squares / row sums
-        int* const xi = part_i + grp * 8;
-        const uint32_t grp_bar = part_bar + 8 * grp;
+        float* const xf = part_f + set0 * 4;          // [group of the set][quadrant]: partial sums of squares ...
+        int* const xi = part_i + set0 * 4;            // ... and row sums
+        const uint32_t grp_bar = part_bar + 8 * set0;
+        const int q0 = P == 1 ? tok_in_tile * (nb >> 5) : 0;         // first partial of this row's token
+        const int nq = P == 1 ? (nb + 31) >> 5 : 4 * P;              // and how many there are
         const uint32_t t_row = tmem_acc + ((uint32_t)(quad * 32) << 16) + grp * 128;
         uint32_t jt = 0;  // tiles this group has done
         bool ok = true;
-        for (int tile = blockIdx.x + grp * gridDim.x; tile < num_tiles && ok; tile += NUM_ACC * gridDim.x, ++jt) {
-            const int token = tile * T + tok_in_tile;
+        for (;; ++jt) {  // this group's tiles are it = grp + 4 jt
+            const int unit = blockIdx.x + (int)((grp + NUM_ACC * jt) / P) * gridDim.x;
+            if (unit >= num_units) break;
+            const int token = P == 1 ? unit * T + tok_in_tile : unit;
             const bool valid = row_in_tile && token < p.M;
             ok = mbar_wait(tmem_full + 8 * grp, jt & 1u, 26);
             ok = __all_sync(0xffffffffu, ok);
@@ -252,15 +265,14 @@ hadamard_quant_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const RowPa
             for (int m = g_rows >> 1; m > 0; m >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, m);
             float tot = ssq;
             if (cross) {  // warp-uniform
-                if (lane == 0) xf[quad] = ssq;
+                if (lane == 0) xf[part * 4 + quad] = ssq;
                 __syncwarp();
                 if (lane == 0) mbar_arrive(grp_bar);
                 ok = mbar_wait(grp_bar, 0u, 27);  // two rendezvous per tile: phases 2 jt and 2 jt + 1
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-                const int q0 = tok_in_tile * (nb >> 5), nq = (nb + 31) >> 5;
                 double t2 = 0.0;
-                for (int q = 0; q < nq; ++q) t2 += (double)xf[(q0 + q) & 3];
+                for (int q = 0; q < nq; ++q) t2 += (double)xf[(q0 + q) & 15];
                 tot = (float)t2;
             }
             const __nv_bfloat16 sb = __float2bfloat16_rn(quest_scale_from_mean_square(__fdiv_rn(tot, (float)K)));
@@ -319,15 +331,14 @@ hadamard_quant_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const RowPa
             // ---- row sums ----
             for (int m = g_rows >> 1; m > 0; m >>= 1) rs16 += __shfl_xor_sync(0xffffffffu, rs16, m);
             if (cross) {
-                if (lane == 0) xi[quad] = rs16;
+                if (lane == 0) xi[part * 4 + quad] = rs16;
                 __syncwarp();
                 if (lane == 0) mbar_arrive(grp_bar);
                 ok = mbar_wait(grp_bar, 1u, 28);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-                const int q0 = tok_in_tile * (nb >> 5), nq = (nb + 31) >> 5;
                 int t2 = 0;
-                for (int q = 0; q < nq; ++q) t2 += xi[(q0 + q) & 3];
+                for (int q = 0; q < nq; ++q) t2 += xi[(q0 + q) & 15];
                 rs16 = t2;
             }
             if (valid && blk == 0 && p.row_sum != nullptr) p.row_sum[token] = rs16 >> 4;  // exact: every term is a multiple of 16
@@ -366,18 +377,38 @@ static int make_block_map(CUtensorMap* map, const void* base, long long rows) {
 
 // Shapes the tensor-core kernel takes: K a multiple of 128 (256 for block 256) with at least 85 % of the 128 tile
 // rows holding whole tokens; everything else stays with hadamard_quant_mma_kernel.
+// Tiling of a row length: P tiles per token (1, 2 or 4) and, for P = 1, T tokens per tile.  False if no tiling keeps at
+// least 85 % of the 128 tile rows busy.
+static bool hq_tc_tiling(int K, int* T_out, int* P_out) {
+    const int nb = K / 128;
+    int T = 1, P = 1;
+    if (nb <= 128) {
+        T = 128 / nb;
+        if (nb < 32 && (nb & (nb - 1)) != 0) return false;  // several tokens per warp need power-of-two groups
+        if (nb >= 32 && T > 1 && nb % 32 != 0) return false;
+    } else if (nb % 2 == 0 && nb / 2 <= 128) {
+        P = 2;
+    } else if (nb % 4 == 0 && nb / 4 <= 128) {
+        P = 4;
+    } else {
+        return false;
+    }
+    const int rows = P == 1 ? T * nb : nb / P;
+    if (rows * 100 < 85 * 128) return false;
+    *T_out = T;
+    *P_out = P;
+    return true;
+}
+
 static bool hq_tc_eligible(const RowParams& p, int block) {
     if (p.K % 128 != 0 || (block == 256 && p.K % 256 != 0)) return false;
-    const int nb = p.K / 128;
-    if (nb > 128) return false;
-    const int T = 128 / nb;
-    if (T * nb * 100 < 85 * 128) return false;
-    if (nb < 32 && (nb & (nb - 1)) != 0) return false;  // several tokens per warp need power-of-two groups
-    if (nb >= 32 && T > 1 && nb % 32 != 0) return false;
+    int T, P;
+    if (!hq_tc_tiling(p.K, &T, &P)) return false;
+    if (block == 256 && P > 1 && ((p.K / 128 / P) & 1)) return false;  // a 256 block must not straddle two tiles
     if (p.q_packed == nullptr || p.scale_out == nullptr || p.scale_in != nullptr || p.q_dense != nullptr ||
         p.x_out != nullptr || !p.quantize)
         return false;
-    if ((long long)p.M * nb >= (1ll << 31)) return false;
+    if ((long long)p.M * (p.K / 128) >= (1ll << 31)) return false;
     return aligned16(p.x) && aligned16(p.q_packed);
 }
 
@@ -397,12 +428,13 @@ static int launch_hq_tc(const RowParams& p, cudaStream_t stream) {
     int sms = 148;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
     const int nb = p.K / 128;
-    const int T = 128 / nb;
-    const int num_tiles = (p.M + T - 1) / T;
+    int T = 1, P = 1;
+    if (!hq_tc_tiling(p.K, &T, &P)) return QB200_ERR_UNSUPPORTED;
+    const int num_units = P == 1 ? (p.M + T - 1) / T : p.M;
     CUtensorMap map;
     const int st = make_block_map(&map, p.x, (long long)p.M * nb);
     if (st != QB200_OK) return st;
-    const int grid = num_tiles < sms ? num_tiles : sms;
-    kernel<<<grid, tc::kThreads, tc::SMEM_BYTES, stream>>>(map, p, nb, T, num_tiles);
+    const int grid = num_units < sms ? num_units : sms;
+    kernel<<<grid, tc::kThreads, tc::SMEM_BYTES, stream>>>(map, p, nb, T, P, num_units);
     return launch_status();
 }

@@ -140,7 +140,8 @@ def check_hadamard_quantize(x: torch.Tensor, block: int) -> tuple[int, int, int]
 # "tc": the tcgen05 kernel where the shape fits its tiling (it must: the call fails otherwise); "mma": the CUDA-core
 # kernel with mma.sync for the 16-point factor; "auto": what the library picks.
 HQ_TC_SHAPES = [("student", 128, 4096), ("laplace", 64, 8192), ("randn", 33, 14336), ("outlier", 7, 2048),
-                ("randn", 1, 256), ("student", 300, 512), ("laplace", 5, 16384), ("randn", 1000, 128)]
+                ("randn", 1, 256), ("student", 300, 512), ("laplace", 5, 16384), ("randn", 1000, 128),
+                ("randn", 5, 28672), ("student", 3, 32768), ("laplace", 2, 65536)]  # tokens spanning 2 and 4 tiles
 
 
 @pytest.mark.parametrize("block", [64, 128, 256])

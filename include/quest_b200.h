@@ -151,6 +151,24 @@ int fused_matmul_dequantize_int4_int4t_bf16_push_cuda(void* const* mat_d_list, i
                                                       cudaStream_t stream);
 
 /*
+ * The int8-operand route of the layer (no counterpart in the reference; an internal format between this library's
+ * two kernels).  hadamard_quantize_a8_cuda_bf16 is hadamard_quantize_int4_cuda_bf16 with another output: instead of
+ * packed int4 it writes the operand the GEMM's tensor cores consume - int8 = 16 x code, [batch_size, group_size]
+ * row-major, and inside every group of 32 consecutive K positions the 16 even positions first, then the 16 odd
+ * ones - so that the GEMM need not unpack A.  Only shapes the tcgen05 quantiser can tile (group_size a multiple of
+ * 128, see quest_b200_prefers_a8); QB200_ERR_UNSUPPORTED otherwise.  fused_matmul_dequantize_a8_int4t_bf16_cuda is the
+ * fused GEMM + epilogue taking that operand (mat_b stays packed int4; K a multiple of 128; always the 256 x 256 tile
+ * kernel).  quest_b200_prefers_a8 returns 1 where this route is the faster one for an [M, K] x [N, K]^T layer (what
+ * quest_b200.layer.linear_forward asks before choosing), else 0; QB200_A8=0|1 in the environment overrides it.
+ */
+int hadamard_quantize_a8_cuda_bf16(void* a8_ptr, void* scale_ptr, void* x_int_row_sum_ptr, const void* x_ptr,
+                                   int group_size, int batch_size, int block, cudaStream_t stream);
+int fused_matmul_dequantize_a8_int4t_bf16_cuda(void* mat_d, const void* mat_a8, const void* mat_b,
+                                               const void* vec_a_add, const void* vec_b_add, const void* vec_a_mul,
+                                               const void* vec_b_mul, int M, int K, int N, cudaStream_t stream);
+int quest_b200_prefers_a8(int M, int K, int N);
+
+/*
  * Fused block-Hadamard + scale + int4 quantise + pack + row-sum of bf16 activations, one pass over
  * x.  Per row: xh = bf16(H_block . x) blockwise along K (Sylvester order, entries +-bf16(block^-0.5)),
  * scale = find_scale(xh), codes = quantize(xh, scale).  Replaces the three launches of the reference's

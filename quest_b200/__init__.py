@@ -228,6 +228,60 @@ def hadamard_quantize_int4(
     return x_int_packed, scale, x_int_row_sum
 
 
+def prefers_a8(m: int, k: int, n: int) -> bool:
+    """Whether the int8-operand route (``hadamard_quantize_a8`` + ``fused_matmul_dequantize_a8``) is the faster one
+    for a layer of this shape."""
+    return bool(_lib.load().quest_b200_prefers_a8(int(m), int(k), int(n)))
+
+
+def hadamard_quantize_a8(
+        x: torch.Tensor,
+        block: int = 128,
+        x_a8: torch.Tensor = None,
+        scale: torch.Tensor = None,
+        x_int_row_sum: torch.Tensor = None,
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """``hadamard_quantize_int4`` with the codes written as the GEMM's int8 operand (16 x code, even positions of every
+    32-group first) instead of packed int4.  Returns (x_a8 [M,K] u8, scale [M,1] bf16, x_int_row_sum [M,1] i32)."""
+    assert x.dim() == 2
+    m, k = x.shape
+    if x_a8 is None:
+        x_a8 = torch.empty(m, k, dtype=torch.uint8, device=x.device)
+    if scale is None:
+        scale = torch.empty(m, 1, dtype=x.dtype, device=x.device)
+    if x_int_row_sum is None:
+        x_int_row_sum = torch.empty(m, 1, dtype=torch.int32, device=x.device)
+    assert x.dtype == torch.bfloat16 and scale.dtype == torch.bfloat16 and x_a8.dtype == torch.uint8 and x_int_row_sum.dtype == torch.int32
+    assert x.is_contiguous() and scale.is_contiguous() and x_a8.is_contiguous() and x_int_row_sum.is_contiguous()
+    assert x_a8.shape == (m, k)
+    dev = _lib.require_cuda(x, scale, x_a8, x_int_row_sum)
+    _call("hadamard_quantize_a8_cuda_bf16", dev, _lib.ptr(x_a8), _lib.ptr(scale), _lib.ptr(x_int_row_sum), _lib.ptr(x), k, m,
+          int(block), _lib.stream_of(x))
+    return x_a8, scale, x_int_row_sum
+
+
+def fused_matmul_dequantize_a8(
+        mat_a8: torch.Tensor,
+        mat_b: torch.Tensor,
+        vec_a_add: torch.Tensor,
+        vec_b_add: torch.Tensor,
+        vec_a_mul: torch.Tensor,
+        vec_b_mul: torch.Tensor,
+        out: torch.Tensor = None,
+) -> torch.Tensor:
+    """``fused_matmul_dequantize_int4_int4t_bf16`` with the A operand as written by ``hadamard_quantize_a8``."""
+    if out is None:
+        out = torch.empty(mat_a8.size(0), mat_b.size(0), dtype=torch.bfloat16, device=mat_a8.device)
+    assert mat_a8.dtype == torch.uint8 and mat_b.dtype == torch.uint8 and vec_a_add.dtype == torch.int32 and vec_b_add.dtype == torch.int32 and vec_a_mul.dtype == torch.bfloat16 and vec_b_mul.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    assert mat_a8.is_contiguous() and mat_b.is_contiguous() and vec_a_add.is_contiguous() and vec_b_add.is_contiguous() and vec_a_mul.is_contiguous() and vec_b_mul.is_contiguous() and out.is_contiguous()
+    assert mat_a8.size(1) == mat_b.size(1) * 2 and out.shape == (mat_a8.size(0), mat_b.size(0))
+    dev = _lib.require_cuda(mat_a8, mat_b, vec_a_add, vec_b_add, vec_a_mul, vec_b_mul, out)
+    _call("fused_matmul_dequantize_a8_int4t_bf16_cuda", dev, _lib.ptr(out), _lib.ptr(mat_a8), _lib.ptr(mat_b),
+          _lib.ptr(vec_a_add), _lib.ptr(vec_b_add), _lib.ptr(vec_a_mul), _lib.ptr(vec_b_mul), mat_a8.size(0),
+          mat_a8.size(1), mat_b.size(0), _lib.stream_of(mat_a8))
+    return out
+
+
 def hadamard_transform(x: torch.Tensor, block: int = 128, weight_side: bool = False, out: torch.Tensor = None) -> torch.Tensor:
     """bf16(H_block @ x) blockwise along the last dim.  ``weight_side`` selects the exact fp32
     normalisation of gemm-quest/benchmarks/utils.py:39 instead of the bf16 one of utils.py:17."""

@@ -25,6 +25,9 @@ SIGNATURES = {
     "fused_matmul_dequantize_int4_int4t_bf16_strided_cuda": [_P, _LL, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     "fused_matmul_dequantize_int4_int4t_bf16_push_cuda": [ctypes.POINTER(ctypes.c_void_p), _I, _LL, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     "hadamard_quantize_int4_cuda_bf16": [_P, _P, _P, _P, _I, _I, _I, _P],
+    "hadamard_quantize_a8_cuda_bf16": [_P, _P, _P, _P, _I, _I, _I, _P],
+    "fused_matmul_dequantize_a8_int4t_bf16_cuda": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
+    "quest_b200_prefers_a8": [_I, _I, _I],
     "hadamard_transform_cuda_bf16": [_P, _P, _I, _I, _I, _I, _P],
     "quest_b200_device_status": [ctypes.POINTER(ctypes.c_int)],
     "quest_b200_version": [],

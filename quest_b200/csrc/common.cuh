@@ -30,6 +30,9 @@ inline int launch_status() {
 // Reads and clears the device status word of the row-kernel translation unit (see tcgen05.cuh).
 int hq_tc_fetch_and_clear_device_status(int* out);
 
+// Whether the tcgen05 quantiser can tile rows of K elements (block 128).
+bool hq_tc_shape_ok(int K);
+
 // ---------------------------------------------------------------------------------------------
 // Device-side helpers
 // ---------------------------------------------------------------------------------------------

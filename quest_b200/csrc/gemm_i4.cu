@@ -580,7 +580,8 @@ constexpr int kPushWarps = 2, kFirstPush = kFirstUnpack + kUnpackWarps;
 constexpr int kWarps = kFirstPush + kPushWarps;
 constexpr int kThreads = kWarps * 32;
 constexpr int VEC_BYTES = TN * 8;
-constexpr int NUM_BARS = 2 * P_STAGES + 2 * U_STAGES + 2 + 1 + 4;
+constexpr int A_STAGES = 3;  // A8 variant: ring of the int8 A tiles (two in the A halves of the int8 stages, one behind the packed B ring)
+constexpr int NUM_BARS = 2 * P_STAGES + 2 * U_STAGES + 2 + 1 + 4 + 2 * A_STAGES;
 constexpr int LAYOUT_BYTES = U_STAGES * U_BYTES + P_STAGES * P_BYTES + VEC_BYTES + NUM_BARS * 8 + 16;
 constexpr int SMEM_BYTES = 232448;  // all the shared memory one CTA can have; the layout needs a 1024-byte aligned start
 static_assert(LAYOUT_BYTES <= SMEM_BYTES, "layout does not fit");
@@ -614,8 +615,11 @@ __device__ __noinline__ void push_tile_rows(const EpilogueParams& ep, int m0, in
 
 // PUSH: the multi-GPU variant (two more warps that copy finished tiles to the peers, helped by the epilogue warps on
 // a CTA's last tile); the single-GPU instantiation carries none of that code and is launched without those warps.
-template <bool FUSED, bool PUSH>
-__global__ void __launch_bounds__(PUSH ? wide::kThreads : wide::kThreads - 32 * wide::kPushWarps, 1)
+// A8 (single GPU only): the A operand arrives already as int8 in operand order (see hadamard_quant_tc_kernel<HB, true>):
+// one more warp copies its tiles with TMA (128-byte swizzle) straight into the int8 ring, the unpack warps handle
+// only B, and the main loop is bound by the MMAs instead of the unpack.
+template <bool FUSED, bool PUSH, bool A8 = false>
+__global__ void __launch_bounds__(PUSH ? wide::kThreads : (A8 ? wide::kThreads - 32 : wide::kThreads - 32 * wide::kPushWarps), 1)
 gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ EpilogueParams ep, const int M, const int N, const int K) {
     using namespace wide;
@@ -639,8 +643,13 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const uint32_t mma_done = tmem_empty + 8;
     const uint32_t out_ready = mma_done + 8;    // [2]
     const uint32_t push_free = out_ready + 16;  // [2]
-    const uint32_t tmem_slot = push_free + 16;
+    const uint32_t full_a = push_free + 16;      // [A_STAGES] A8 only
+    const uint32_t empty_a = full_a + 8 * A_STAGES;
+    const uint32_t tmem_slot = empty_a + 8 * A_STAGES;
     volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - raw_base));
+    // A8: packed B stages are compact (TN * 64 bytes each), which leaves room for a third A slot behind them
+    constexpr int PB_BYTES = A8 ? TN * PK_ROW : P_BYTES;
+    auto a_slot = [&](uint32_t sa) { return sa < 2 ? u_base + sa * U_BYTES : p_base + P_STAGES * (TN * PK_ROW); };
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -658,6 +667,10 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         for (int i = 0; i < U_STAGES; ++i) {
             mbar_init(full_u + 8 * i, kUnpackWarps);
             mbar_init(empty_u + 8 * i, 1);
+        }
+        for (int i = 0; i < A_STAGES; ++i) {
+            mbar_init(full_a + 8 * i, 1);
+            mbar_init(empty_a + 8 * i, 1);
         }
         mbar_init(tmem_full, 1);
         mbar_init(tmem_empty, kEpiWarps);
@@ -680,7 +693,7 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
-            tma_prefetch_desc(&tmap_a);
+            if (!A8) tma_prefetch_desc(&tmap_a);
             tma_prefetch_desc(&tmap_b);
             uint32_t it = 0;
             bool ok = true;
@@ -690,10 +703,10 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const uint32_t s = it % P_STAGES, ph = (it / P_STAGES) & 1u;
                     if (!(ok = mbar_wait(empty_p + 8 * s, ph ^ 1u, 1))) break;
-                    mbar_arrive_expect_tx(full_p + 8 * s, P_BYTES);
-                    const uint32_t dst = p_base + s * P_BYTES;
-                    tma_load_2d(dst, &tmap_a, kb * PK_ROW, m0, full_p + 8 * s);
-                    tma_load_2d(dst + TM * PK_ROW, &tmap_b, kb * PK_ROW, n0, full_p + 8 * s);
+                    mbar_arrive_expect_tx(full_p + 8 * s, PB_BYTES);
+                    const uint32_t dst = p_base + s * PB_BYTES;
+                    if (!A8) tma_load_2d(dst, &tmap_a, kb * PK_ROW, m0, full_p + 8 * s);
+                    tma_load_2d(A8 ? dst : dst + TM * PK_ROW, &tmap_b, kb * PK_ROW, n0, full_p + 8 * s);
                 }
             }
             const uint32_t pending = it < (uint32_t)P_STAGES ? it : (uint32_t)P_STAGES;
@@ -717,8 +730,13 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     if (!(ok = mbar_wait(full_u + 8 * s, ph, 4))) break;
                     tc_fence_after();
                     if (it == 0) QB_TRACE(1);
-                    const uint32_t a_addr = u_base + s * U_BYTES;
-                    const uint32_t b_addr = a_addr + TM * U8_ROW;
+                    const uint32_t sa = it % A_STAGES;
+                    if (A8) {
+                        if (!(ok = mbar_wait(full_a + 8 * sa, (it / A_STAGES) & 1u, 21))) break;
+                        tc_fence_after();
+                    }
+                    const uint32_t a_addr = A8 ? a_slot(sa) : u_base + s * U_BYTES;
+                    const uint32_t b_addr = u_base + s * U_BYTES + TM * U8_ROW;
 #pragma unroll
                     for (int j = 0; j < BK / 32; ++j) {
                         const uint64_t db = make_smem_desc(b_addr + 32 * j);
@@ -727,6 +745,7 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                             umma_i8(tmem_acc + TN, make_smem_desc(a_addr + 128 * U8_ROW + 32 * j), db, IDESC, (kb | j) != 0 ? 1u : 0u);
                     }
                     umma_commit(empty_u + 8 * s);
+                    if (A8) umma_commit(empty_a + 8 * sa);
                 }
                 if (ok) umma_commit(tmem_full);
             }
@@ -805,6 +824,27 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 }
             }
         }
+    } else if (A8 && warp == kFirstPush) {
+        // ------------------------------ A operand producer (A8 only; there are no push warps then) -----------
+        if (lane == 0) {
+            tma_prefetch_desc(&tmap_a);
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % tiles_m) * TM;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const uint32_t sa = it % A_STAGES, aph = (it / A_STAGES) & 1u;
+                    if (!(ok = mbar_wait(empty_a + 8 * sa, aph ^ 1u, 19))) break;
+                    mbar_arrive_expect_tx(full_a + 8 * sa, TM * U8_ROW);
+                    tma_load_2d(a_slot(sa), &tmap_a, kb * U8_ROW, m0, full_a + 8 * sa);
+                }
+            }
+            const uint32_t pending = it < (uint32_t)A_STAGES ? it : (uint32_t)A_STAGES;
+            for (uint32_t j = 0; j < pending; ++j) {  // do not leave while a copy of ours may still land
+                const uint32_t i2 = it - 1 - j;
+                mbar_wait(full_a + 8 * (i2 % A_STAGES), (i2 / A_STAGES) & 1u, 20);
+            }
+        }
     } else if (warp >= kFirstPush) {
         // ------------------------------ push warps (multi-GPU only) ------------------------------
         if (PUSH) {
@@ -839,11 +879,11 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 ok = mbar_wait(full_p + 8 * ps, pph, 7) && mbar_wait(empty_u + 8 * us, uph ^ 1u, 8);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-                const uint32_t src = p_base + ps * P_BYTES;
+                const uint32_t src = A8 ? p_base + ps * PB_BYTES - TM * PK_ROW : p_base + ps * P_BYTES;  // rows are numbered from the A rows on
                 const uint32_t dst = u_base + us * U_BYTES;
                 constexpr int ITEMS = (TM + TN) * 4 / (kUnpackWarps * 32);  // 8
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
+                for (int h = A8 ? 1 : 0; h < 2; ++h) {  // the first half of the items are the A rows
                     uint4 pk[ITEMS / 2];
 #pragma unroll
                     for (int i = 0; i < ITEMS / 2; ++i) {
@@ -1018,6 +1058,40 @@ static int pick_splits(int M, int N, int K, int sms) {
     if (s > num_kb / 2) s = num_kb / 2;
     if (s > 16) s = 16;
     return s >= 2 ? (int)s : 1;
+}
+
+// A operand as int8 [rows, K] row-major; box = 128 bytes (one K stage, the swizzle span) x 256 rows.
+static int make_a8_map(CUtensorMap* map, const void* base, int rows, int K) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (fn == nullptr) return QB200_ERR_DRIVER;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)K};
+    const cuuint32_t box[2] = {(cuuint32_t)U8_ROW, (cuuint32_t)wide::TM};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? QB200_OK : QB200_ERR_DRIVER;
+}
+
+static int launch_gemm_wide_a8(const EpilogueParams& ep, const void* a8, const void* b, int M, int K, int N, int sms,
+                               int dev, cudaStream_t stream) {
+    static bool attr_set[64] = {false};
+    auto kernel = gemm_i4_wide_kernel<true, false, true>;
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, wide::SMEM_BYTES) != cudaSuccess)
+            return QB200_ERR_CUDA;
+        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
+    CUtensorMap ma, mb;
+    int st = make_a8_map(&ma, a8, M, K);
+    if (st != QB200_OK) return st;
+    st = make_packed_map(&mb, b, N, K, wide::TN);
+    if (st != QB200_OK) return st;
+    const int tiles = ((M + wide::TM - 1) / wide::TM) * ((N + wide::TN - 1) / wide::TN);
+    const int grid = tiles < sms ? tiles : sms;
+    kernel<<<grid, wide::kThreads - 32, wide::SMEM_BYTES, stream>>>(ma, mb, ep, M, N, K);
+    return launch_status();
 }
 
 template <bool FUSED, bool PUSH>
@@ -1227,6 +1301,46 @@ extern "C" int fused_matmul_dequantize_int4_int4t_bf16_push_cuda(void* const* ma
     ep.a_mul = static_cast<const __nv_bfloat16*>(vec_a_mul);
     ep.b_mul = static_cast<const __nv_bfloat16*>(vec_b_mul);
     return run_gemm(true, ep, mat_a, mat_b, M, K, N, stream);
+}
+
+extern "C" int fused_matmul_dequantize_a8_int4t_bf16_cuda(void* mat_d, const void* mat_a8, const void* mat_b,
+                                                          const void* vec_a_add, const void* vec_b_add,
+                                                          const void* vec_a_mul, const void* vec_b_mul, int M, int K,
+                                                          int N, cudaStream_t stream) {
+    if (M < 0 || N < 0 || K < 0) return QB200_ERR_INVALID_ARGUMENT;
+    if (M == 0 || N == 0) return QB200_OK;
+    if (!mat_d || !mat_a8 || !mat_b || !vec_a_add || !vec_b_add || !vec_a_mul || !vec_b_mul) return QB200_ERR_INVALID_ARGUMENT;
+    if (K == 0 || K % 128 != 0 || K >= (1 << 17)) return QB200_ERR_UNSUPPORTED;
+    if (!aligned16(mat_a8) || !aligned16(mat_b)) return QB200_ERR_INVALID_ARGUMENT;
+    EpilogueParams ep{};
+    ep.out = mat_d;
+    ep.ld = N;
+    ep.a_add = static_cast<const int32_t*>(vec_a_add);
+    ep.b_add = static_cast<const int32_t*>(vec_b_add);
+    ep.a_mul = static_cast<const __nv_bfloat16*>(vec_a_mul);
+    ep.b_mul = static_cast<const __nv_bfloat16*>(vec_b_mul);
+    ep.vec_ok = aligned16(mat_d) && (N % 8 == 0);
+    if (ep.vec_ok && (reinterpret_cast<uintptr_t>(mat_d) & 31u) == 0 && N % 16 == 0) ep.vec_ok = 2;
+    int dev = 0;
+    const int sms = sm_count_of_current_device(&dev);
+    if (sms <= 0) return QB200_ERR_CUDA;
+    return launch_gemm_wide_a8(ep, mat_a8, mat_b, M, K, N, sms, dev, stream);
+}
+
+constexpr bool kA8ByDefault = false;  // the route is chosen only on request (QB200_A8=1) until it measures faster everywhere
+
+// 1 if, for this layer shape, the int8-operand route (hadamard_quantize_a8_cuda_bf16 + the GEMM above) is the faster one:
+// the 256 x 256 kernel would be chosen anyway and the quantiser's tcgen05 kernel can tile K.
+extern "C" int quest_b200_prefers_a8(int M, int K, int N) {
+    if (M <= 0 || K <= 0 || N <= 0 || K % 128 != 0 || K >= (1 << 17)) return 0;
+    if (getenv("QB200_GEMM_TILE") != nullptr || getenv("QB200_GEMM_SPLITS") != nullptr) return 0;
+    if (const char* e = getenv("QB200_A8")) return e[0] != '0';
+    if (!kA8ByDefault) return 0;
+    int dev = 0;
+    const int sms = sm_count_of_current_device(&dev);
+    long long est = 0;
+    if (sms <= 0 || pick_tile(M, N, K, sms, &est) != kWideTile) return 0;
+    return hq_tc_shape_ok(K) ? 1 : 0;
 }
 
 extern "C" int fused_matmul_dequantize_int4_int4t_bf16_noalloc_cuda(void* mat_d, const void* mat_a, const void* mat_b,

@@ -49,7 +49,10 @@ __device__ __forceinline__ void pair_rows(uint32_t (&r)[16], int lane) {
 // nb: 128-element blocks per token (K / 128).  A unit is what a reduction needs together: T whole tokens in one tile
 // (P = 1, T * nb <= 128 rows), or one token spread over P = 2 or 4 consecutive tiles of nb / P rows (K > 16384), which
 // P neighbouring drain groups then process side by side.
-template <int HB>
+// A8: instead of packed int4, write the operand the GEMM's tensor cores consume, so that the GEMM need not unpack A:
+// int8 = 16 x code, [M, K] row-major, and inside every group of 32 consecutive K positions the 16 even positions
+// first, then the 16 odd ones - the order in which the GEMM's own unpack lays out the codes of a 16-byte packed piece.
+template <int HB, bool A8>
 __global__ void __launch_bounds__(tc::kThreads, 1)
 hadamard_quant_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const RowParams p, const int nb, const int T,
                          const int P, const int num_units) {
@@ -285,10 +288,10 @@ hadamard_quant_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const RowPa
             if (valid && blk == 0) p.scale_out[token] = sb;
 
             // ---- pass 2: quantise and pack; a piece is 16 columns of bf16 pairs = 32 elements = 16 packed bytes ----
-            uint8_t* const dst = p.q_packed + (size_t)token * (K >> 1) + blk * 64;
+            uint8_t* const dst = A8 ? p.q_a8 + (size_t)token * K + blk * 128 : p.q_packed + (size_t)token * (K >> 1) + blk * 64;
             int rs16 = 0;
             auto quantise32 = [&](const uint32_t (&v)[16], int piece) {
-                uint32_t w[4];
+                uint32_t w[4], wo[4];
 #pragma unroll
                 for (int q8 = 0; q8 < 4; ++q8) {  // eight elements -> one 32-bit word
                     uint32_t ub[8];
@@ -306,12 +309,25 @@ hadamard_quant_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const RowPa
                     // byte j of the word = (code[2j+1] << 4) | code[2j]
                     const uint32_t ev = __byte_perm(__byte_perm(ub[0], ub[2], 0x0040), __byte_perm(ub[4], ub[6], 0x0040), 0x5410);
                     const uint32_t od = __byte_perm(__byte_perm(ub[1], ub[3], 0x0040), __byte_perm(ub[5], ub[7], 0x0040), 0x5410);
-                    w[q8] = (ev & 0x0F0F0F0Fu) | ((od << 4) & 0xF0F0F0F0u);
+                    if (A8) {
+                        w[q8] = (ev << 4) & 0xF0F0F0F0u;   // 16 x the codes at even positions
+                        wo[q8] = (od << 4) & 0xF0F0F0F0u;  // 16 x the codes at odd positions
+                    } else {
+                        w[q8] = (ev & 0x0F0F0F0Fu) | ((od << 4) & 0xF0F0F0F0u);
+                    }
                 }
                 if (valid) {
+                    if (A8) {
 #pragma unroll
-                    for (int q8 = 0; q8 < 4; ++q8) rs16 = nibble_sum16(w[q8], rs16);
-                    *reinterpret_cast<uint4*>(dst + 16 * piece) = make_uint4(w[0], w[1], w[2], w[3]);
+                        for (int q8 = 0; q8 < 4; ++q8)
+                            rs16 = __dp4a((int)wo[q8], 0x01010101, __dp4a((int)w[q8], 0x01010101, rs16));
+                        *reinterpret_cast<uint4*>(dst + 32 * piece) = make_uint4(w[0], w[1], w[2], w[3]);
+                        *reinterpret_cast<uint4*>(dst + 32 * piece + 16) = make_uint4(wo[0], wo[1], wo[2], wo[3]);
+                    } else {
+#pragma unroll
+                        for (int q8 = 0; q8 < 4; ++q8) rs16 = nibble_sum16(w[q8], rs16);
+                        *reinterpret_cast<uint4*>(dst + 16 * piece) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
                 }
             };
 #pragma unroll
@@ -405,19 +421,19 @@ static bool hq_tc_eligible(const RowParams& p, int block) {
     int T, P;
     if (!hq_tc_tiling(p.K, &T, &P)) return false;
     if (block == 256 && P > 1 && ((p.K / 128 / P) & 1)) return false;  // a 256 block must not straddle two tiles
-    if (p.q_packed == nullptr || p.scale_out == nullptr || p.scale_in != nullptr || p.q_dense != nullptr ||
-        p.x_out != nullptr || !p.quantize)
+    if ((p.q_packed == nullptr) == (p.q_a8 == nullptr) || p.scale_out == nullptr || p.scale_in != nullptr ||
+        p.q_dense != nullptr || p.x_out != nullptr || !p.quantize)
         return false;
     if ((long long)p.M * (p.K / 128) >= (1ll << 31)) return false;
-    return aligned16(p.x) && aligned16(p.q_packed);
+    return aligned16(p.x) && aligned16(p.q_packed) && aligned16(p.q_a8);
 }
 
-template <int HB>
-static int launch_hq_tc(const RowParams& p, cudaStream_t stream) {
+template <int HB, bool A8>
+static int launch_hq_tc_impl(const RowParams& p, cudaStream_t stream) {
     static bool attr_set[64] = {false};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return QB200_ERR_CUDA;
-    auto kernel = hadamard_quant_tc_kernel<HB>;
+    auto kernel = hadamard_quant_tc_kernel<HB, A8>;
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM_BYTES) != cudaSuccess) {
             cudaGetLastError();
@@ -437,4 +453,9 @@ static int launch_hq_tc(const RowParams& p, cudaStream_t stream) {
     const int grid = num_units < sms ? num_units : sms;
     kernel<<<grid, tc::kThreads, tc::SMEM_BYTES, stream>>>(map, p, nb, T, P, num_units);
     return launch_status();
+}
+
+template <int HB>
+static int launch_hq_tc(const RowParams& p, cudaStream_t stream) {
+    return p.q_a8 != nullptr ? launch_hq_tc_impl<HB, true>(p, stream) : launch_hq_tc_impl<HB, false>(p, stream);
 }

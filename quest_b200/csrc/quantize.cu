@@ -23,6 +23,7 @@ struct RowParams {
     __nv_bfloat16* scale_out;      // optional [M] computed scale
     int8_t* q_dense;               // optional [M,K]
     uint8_t* q_packed;             // optional [M,K/2]
+    uint8_t* q_a8;                 // optional [M,K]: sixteen times the codes as int8, in the GEMM's operand order (tcgen05 kernel only)
     int32_t* row_sum;              // optional [M]
     int K;
     int M;
@@ -748,6 +749,11 @@ static int launch_row(const RowParams& p, cudaStream_t stream) {
 
 int hq_tc_fetch_and_clear_device_status(int* out) { return fetch_and_clear_device_status(out); }
 
+bool hq_tc_shape_ok(int K) {
+    int T, P;
+    return K % 128 == 0 && hq_tc_tiling(K, &T, &P);
+}
+
 static bool vector_path_ok(const RowParams& p) {
     if (p.K % 8 != 0 || p.K > kMaxVectorK) return false;
     if (!aligned16(p.x)) return false;
@@ -921,6 +927,30 @@ extern "C" int hadamard_quantize_int4_cuda_bf16(void* x_int_packed_ptr, void* sc
         case 64: return launch_hq_mma<64>(p, stream);
         case 128: return launch_hq_mma<128>(p, stream);
         default: return launch_hq_mma<256>(p, stream);
+    }
+}
+
+extern "C" int hadamard_quantize_a8_cuda_bf16(void* a8_ptr, void* scale_ptr, void* x_int_row_sum_ptr, const void* x_ptr,
+                                              int group_size, int batch_size, int block, cudaStream_t stream) {
+    if (group_size < 0 || batch_size < 0) return QB200_ERR_INVALID_ARGUMENT;
+    if (block != 64 && block != 128 && block != 256) return QB200_ERR_UNSUPPORTED;
+    if (batch_size == 0) return QB200_OK;
+    if (a8_ptr == nullptr || scale_ptr == nullptr || x_ptr == nullptr || group_size == 0) return QB200_ERR_INVALID_ARGUMENT;
+    if (group_size % block != 0) return QB200_ERR_INVALID_ARGUMENT;
+    RowParams p{};
+    p.x = static_cast<const __nv_bfloat16*>(x_ptr);
+    p.scale_out = static_cast<__nv_bfloat16*>(scale_ptr);
+    p.q_a8 = static_cast<uint8_t*>(a8_ptr);
+    p.row_sum = static_cast<int32_t*>(x_int_row_sum_ptr);
+    p.K = group_size;
+    p.M = batch_size;
+    p.quantize = 1;
+    p.had_scale = __bfloat162float(__float2bfloat16_rn((float)(1.0 / sqrt((double)block))));
+    if (!hq_tc_eligible(p, block)) return QB200_ERR_UNSUPPORTED;  // only the tcgen05 kernel writes this format
+    switch (block) {
+        case 64: return launch_hq_tc<64>(p, stream);
+        case 128: return launch_hq_tc<128>(p, stream);
+        default: return launch_hq_tc<256>(p, stream);
     }
 }
 

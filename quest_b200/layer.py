@@ -59,10 +59,15 @@ def linear_forward(
         use_hadamard: bool = False,
         backend: str = 'cuda',
         block: int = HADAMARD_BLOCK,
+        _a_int8: torch.Tensor = None,
 ) -> torch.Tensor:
     """out (M, N) bf16 = activation (M, K) @ weight^T in W4A4.  The ``_a_*`` arguments are optional
     caller-owned workspaces (CUDA-graph friendly), as in the reference.  ``_c``, if given, makes the
-    call take the unfused int32 GEMM + add_mul_vv route (the reference's debug mode)."""
+    call take the unfused int32 GEMM + add_mul_vv route (the reference's debug mode).
+
+    With ``use_hadamard`` and a shape for which the library prefers it, the quantiser writes the GEMM's int8 operand
+    directly (``_a_int8`` [M, K] uint8 is its workspace) instead of packed int4: same codes, same result, no unpack
+    of A inside the GEMM.  A caller that passes ``_a_int_packed`` but no ``_a_int8`` keeps the packed route."""
     if w_meta_e is not None:
         raise NotImplementedError("quest_b200 implements the dense W4A4 path only")
     M, K, N = activation.size(0), activation.size(1), w_int_packed.size(0)
@@ -70,8 +75,15 @@ def linear_forward(
     if out is None:
         out = torch.empty(M, N, dtype=dtype, device=device)
     a_scale = torch.empty(M, 1, dtype=dtype, device=device) if _a_scale is None else _a_scale
-    a_int_packed = torch.empty(M, K // 2, dtype=torch.uint8, device=device) if _a_int_packed is None else _a_int_packed
     a_int_row_sum = torch.empty(M, 1, dtype=torch.int32, device=device) if _a_int_row_sum is None else _a_int_row_sum
+    if (use_hadamard and _c is None and (_a_int8 is not None or _a_int_packed is None) and K % block == 0
+            and quest.prefers_a8(M, K, N)):
+        a_int8 = torch.empty(M, K, dtype=torch.uint8, device=device) if _a_int8 is None else _a_int8
+        quest.hadamard_quantize_a8(activation, block=block, x_a8=a_int8, scale=a_scale, x_int_row_sum=a_int_row_sum)
+        quest.fused_matmul_dequantize_a8(mat_a8=a_int8, mat_b=w_int_packed, vec_a_add=a_int_row_sum, vec_b_add=w_add,
+                                         vec_a_mul=a_scale, vec_b_mul=w_scale, out=out)
+        return out
+    a_int_packed = torch.empty(M, K // 2, dtype=torch.uint8, device=device) if _a_int_packed is None else _a_int_packed
     if use_hadamard:
         quest.hadamard_quantize_int4(activation, block=block, x_int_packed=a_int_packed, scale=a_scale,
                                      x_int_row_sum=a_int_row_sum)

@@ -584,3 +584,46 @@ def test_checkpoint_conversion_matches_oracle_and_module_swap():
     for blk_a, blk_b in zip(a.transformer["h"], b.transformer["h"]):
         assert blk_a.mlp.c_proj(blk_a.mlp.w1(x)).equal(blk_b.mlp.c_proj(blk_b.mlp.w1(x)))
         assert blk_a.attn.c_attn(x).equal(blk_b.attn.c_attn(x))
+
+
+# ------------------------------------------------------------------ int8-operand route ----------------
+@pytest.mark.parametrize("block", [64, 128, 256])
+@pytest.mark.parametrize("m,k,n", [(300, 512, 264), (129, 4096, 520), (2048, 4096, 4096), (70, 28672, 256), (1, 128, 8)])
+def test_int8_operand_route_matches_the_packed_route(block, m, k, n, monkeypatch):
+    """hadamard_quantize_a8 writes 16 x the same codes in the GEMM's operand order (even positions of every 32-group
+    first); the GEMM on that operand gives the bits of the packed route and of the oracle epilogue.  Both quantiser
+    calls use the tcgen05 kernel (the only one that writes the int8 operand), so their codes must be identical."""
+    if k % block != 0:
+        pytest.skip("K is not a multiple of the block")
+    monkeypatch.setenv("QB200_HQ_KERNEL", "tc")
+    x = make_activations("student", m, k, seed=m + k).to(DEV)
+    w = (0.02 * torch.randn(n, k, generator=torch.Generator().manual_seed(n))).to(torch.bfloat16).to(DEV)
+    wp, ws, wa, _ = quest.preprocess_weight(w, use_hadamard=True, block=block)
+    packed, scale, rsum = quest.hadamard_quantize_int4(x, block)
+    a8, scale8, rsum8 = quest.hadamard_quantize_a8(x, block)
+    assert scale8.equal(scale) and rsum8.equal(rsum)
+    codes = quest.unpack_int4(packed).view(m, k // 32, 16, 2)                     # [.., position pair, even/odd]
+    expect = torch.cat([codes[..., 0], codes[..., 1]], dim=-1).reshape(m, k)       # evens of a 32-group, then odds
+    assert a8.view(torch.int8).equal((expect * 16).to(torch.int8))
+    ref = quest.fused_matmul_dequantize_int4_int4t_bf16(packed, wp, rsum, wa, scale, ws)
+    got = quest.fused_matmul_dequantize_a8(a8, wp, rsum8, wa, scale8, ws)
+    assert got.equal(ref)
+    cpu = O.fused_matmul_dequantize_int4_int4t_bf16(packed.cpu(), wp.cpu(), rsum.cpu(), wa.cpu(), scale.cpu(), ws.cpu())
+    assert got.cpu().equal(cpu)
+
+
+def test_linear_forward_takes_the_int8_operand_route_where_preferred(monkeypatch):
+    m, k, n = 2048, 4096, 4096
+    x = make_activations("student", m, k, seed=1).to(DEV)
+    w = (0.02 * torch.randn(n, k, generator=torch.Generator().manual_seed(2))).to(torch.bfloat16).to(DEV)
+    wp, ws, wa, _ = quest.preprocess_weight(w, use_hadamard=True)
+    monkeypatch.setenv("QB200_HQ_KERNEL", "tc")  # same quantiser arithmetic on both routes
+    monkeypatch.setenv("QB200_A8", "0")
+    assert not quest.prefers_a8(m, k, n)
+    y_packed = quest.linear_forward(x, wp, ws, wa, use_hadamard=True)
+    monkeypatch.setenv("QB200_A8", "1")
+    assert quest.prefers_a8(m, k, n)
+    y_a8 = quest.linear_forward(x, wp, ws, wa, use_hadamard=True)
+    assert y_a8.equal(y_packed)
+    monkeypatch.delenv("QB200_A8")
+    assert not quest.prefers_a8(16, k, n) and not quest.prefers_a8(m, 5632, n)

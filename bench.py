@@ -173,7 +173,7 @@ def run_reference(args):
         "e2e": {"value": r["tops"], "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line))
+    emit(line)
 
 
 # ----------------------------------------------------------------------------------------------------
@@ -486,7 +486,7 @@ def run_b200(args):
             r = cpu_reference_run(args, steps=5, warmup=1)
             line["cpu_baseline"] = {"value": r["tops"], "unit": "TOPS", "cores": r["cores"], "kind": "port",
                                     "sample": r["sample"], "ms_per_step": r["seconds_per_step"] * 1e3}
-        print(json.dumps(line))
+        emit(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -510,7 +510,7 @@ def run_prefill(args):
         torch.cuda.empty_cache()
     out["value"] = min(out["int4"]["eager_ms"], out["int4"]["graph_ms"])
     out["speedup_vs_bf16"] = min(out["bf16"]["eager_ms"], out["bf16"]["graph_ms"]) / out["value"]
-    print(json.dumps(out))
+    emit(out)
 
 
 def run_sweep(args):
@@ -568,11 +568,31 @@ def run_sweep(args):
                 hq.append({"M": m, "K": k, "block": block, "us": t * 1e6, "gbs": nbytes / t / 1e9,
                            "frac_of_hbm": nbytes / t / 1e9 / peaks["hbm_gbs"]})
             del x, pk
-    print(json.dumps({"workload": "sweep", "peaks": peaks, "linear": linear, "hadamard_quantize": hq}))
+    emit({"workload": "sweep", "peaks": peaks, "linear": linear, "hadamard_quantize": hq})
+
+
+_REAL_STDOUT = None
+
+
+def keep_stdout_for_the_json_line():
+    """Libraries (NCCL's version banner at NCCL_DEBUG=VERSION, for one) write to file descriptor 1.  The contract is
+    ONE JSON line on stdout, so descriptor 1 is pointed at stderr for the whole run and the JSON line is written to a
+    duplicate of the original stdout at the end."""
+    global _REAL_STDOUT
+    sys.stdout.flush()
+    _REAL_STDOUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+
+
+def emit(line: dict) -> None:
+    out = _REAL_STDOUT if _REAL_STDOUT is not None else sys.stdout
+    out.write(json.dumps(line) + "\n")
+    out.flush()
 
 
 def main():
     args = parse_args()
+    keep_stdout_for_the_json_line()
     if args.workload == "prefill":
         run_prefill(args)
         return

@@ -51,6 +51,19 @@ int quest_b200_version(void);
 int quest_b200_device_status(int* status);
 
 /*
+ * Test support: launches the fused GEMM with its TMA producer switched off and the limit of every bounded in-kernel
+ * wait shortened to wait_limit_cycles (SM clock cycles; a few million = a few milliseconds), so that the waits of the
+ * consumer warps run out by construction - no trap, no fault, no unbounded spin.  The kernel records
+ * QB200_ERR_DEVICE_TIMEOUT, releases what it holds and returns; mat_d is not written.  Synchronises the stream and
+ * restores the normal limit before returning.  The caller then reads quest_b200_device_status(), which reports
+ * (site << 8) | QB200_ERR_DEVICE_TIMEOUT once and clears it.  No counterpart in the reference (its kernels have no
+ * waits of this kind).
+ */
+int quest_b200_test_bounded_wait_cuda(void* mat_d, const void* mat_a, const void* mat_b, const void* vec_a_add,
+                                      const void* vec_b_add, const void* vec_a_mul, const void* vec_b_mul, int M, int K,
+                                      int N, long long wait_limit_cycles, cudaStream_t stream);
+
+/*
  * scale[m] = bf16( sqrt(mean_k x[m,k]^2) * (2.513930578568423 * 2 / 15) + 1e-8 )
  * Replaces find_scale_int4_cuda_bf16, gemm-quest/quest/quantize.cpp:5-11
  * (kernel gemm-quest/quest/quantize_kernel.cu:38-117).
@@ -122,13 +135,22 @@ int fused_matmul_dequantize_int4_int4t_bf16_strided_cuda(void* mat_d, long long 
                                                          cudaStream_t stream);
 
 /*
- * The fused GEMM + epilogue for callers that must not trigger any allocation (graph capture, allocator-controlled
- * processes): when it runs the split-K kernel its scratch is a fixed 8 MiB array in device memory (static storage of
- * the library, address taken once per device) instead of the per-device buffer the other entry points allocate on
- * first use.  splits = 0 lets the library choose the number of K ranges (1 = the kernels without scratch), splits
- * >= 2 asks for that many.  Returns QB200_ERR_SCRATCH_LIMIT, and launches nothing, if
- * tiles x splits x rows-per-tile exceeds 8192 (tiles = ceil(M/128) * ceil(N/256), rows-per-tile = min(128, M rounded
- * up to 8)).  One such launch per device may be in flight at a time.  No counterpart in the reference.
+ * The fused GEMM + epilogue for callers that cannot allocate device memory at the time of the call: code that runs
+ * while a stream is being captured, a process whose memory is handed out in full to a framework allocator at start-up,
+ * a real-time loop that may not block in the driver.  The ordinary entry points obtain their split-K scratch with
+ * cudaMalloc on first use; this one keeps it in a fixed 8 MiB array in device memory (static storage of the library,
+ * held by every GPU that loads it until the process exits) and calls no allocating routine on any path.
+ *   splits = 0   the library chooses the number of K ranges and never asks for more than the array holds: where its
+ *                usual choice would not fit it takes fewer ranges, down to 1 (the kernels that need no scratch).
+ *   splits >= 2  that many ranges; QB200_ERR_SCRATCH_LIMIT, and nothing is launched, if
+ *                tiles x splits x rows-per-tile > 8192  (tiles = ceil(M/128) * ceil(N/256),
+ *                rows-per-tile = min(128, M rounded up to 8)), or if there are more than 1024 tiles.
+ *   splits = 1   never split.
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress); make that call before any
+ * stream capture.  All calls on a device share the one array and its tile counters: two split-K launches of this entry
+ * point that overlap on the GPU (different streams) race and corrupt each other's sums - keep them on one stream or
+ * order them with events.  The array is separate from the ordinary entry points' buffer, so a launch of this entry
+ * point may overlap one of theirs.  No counterpart in the reference.
  */
 int fused_matmul_dequantize_int4_int4t_bf16_noalloc_cuda(void* mat_d, const void* mat_a, const void* mat_b,
                                                          const void* vec_a_add, const void* vec_b_add,

@@ -297,4 +297,5 @@ def hadamard_transform(x: torch.Tensor, block: int = 128, weight_side: bool = Fa
     return out
 
 
-from .layer import Linear4bit, linear_forward, preprocess_weight, unpack_int4  # noqa: E402,F401
+from .layer import (Linear4bit, fused_matmul_dequantize_int4_bf16, linear_forward, preprocess_weight,  # noqa: E402,F401
+                    unpack_int4)

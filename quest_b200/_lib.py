@@ -29,6 +29,7 @@ SIGNATURES = {
     "fused_matmul_dequantize_a8_int4t_bf16_cuda": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     "quest_b200_prefers_a8": [_I, _I, _I],
     "hadamard_transform_cuda_bf16": [_P, _P, _I, _I, _I, _I, _P],
+    "quest_b200_test_bounded_wait_cuda": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _LL, _P],
     "quest_b200_device_status": [ctypes.POINTER(ctypes.c_int)],
     "quest_b200_version": [],
 }

@@ -91,6 +91,7 @@ struct EpilogueParams {
     int32_t* scratch;       // [tile * splits + range][slab_rows][256 columns] int32 partial sums
     int slab_ints;          // slab_rows * 256: a slab holds only the rows a tile can have (M rounded up to 8, at most 128)
     int* counters;          // one per output tile, all zero between launches
+    int test_skip_producer; // tests only: the TMA producer issues nothing, so that every bounded wait of the launch runs out
 };
 
 
@@ -181,9 +182,9 @@ __device__ __forceinline__ void unpack_x16(const uint4& pk, uint4& lo, uint4& hi
 // ---------------------------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------------------------
-// SPLIT: a work item is (output tile, K range).  The epilogue adds its shifted int32 partial sums into ep.scratch with
-// integer atomics (exact, order-independent); the CTA that completes a tile (a counter per tile tells) reads the
-// sums back, applies the normal epilogue and leaves scratch and counter zeroed for the next launch.
+// SPLIT: a work item is (output tile, K range).  The epilogue writes its shifted int32 partial sums to the item's own
+// slab of ep.scratch (plain stores, nothing to zero); the CTA that completes a tile (a counter per tile tells) sums the
+// tile's slabs, applies the normal epilogue and resets the counter for the next launch.
 template <int BN, bool FUSED, bool SPLIT = false>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_i4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -207,6 +208,9 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const uint32_t tmem_slot = push_free + 16;
     volatile uint32_t* tmem_slot_ptr =
         reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+    // Set by an epilogue warp whose bounded wait gave up; read by all of them behind the named barrier every one of
+    // them still reaches, so that they leave the tile loop together (none is left waiting at a later named barrier).
+    volatile int* epi_abort = reinterpret_cast<volatile int*>(smem_raw + (tmem_slot + 12 - smem_u32(smem_raw)));
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -242,6 +246,7 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             mbar_init(push_free + 8 * i, kNumPushWarps);
         }
         fence_barrier_init();
+        *epi_abort = 0;
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, C::TMEM_COLS);
@@ -258,7 +263,7 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             tma_prefetch_desc(&tmap_a);
             tma_prefetch_desc(&tmap_b);
             uint32_t it = 0;
-            bool ok = true;
+            bool ok = ep.test_skip_producer == 0;
             for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
                 const int tile = tile_of(item);
                 const int m0 = (tile % tiles_m) * BM;
@@ -341,11 +346,12 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     a_add = ep.a_add[row];
                     half_a_mul = 0.5f * bf16_to_f32(ep.a_mul[row]);
                 }
-                asm volatile("bar.sync 1, %0;" ::"n"(kNumEpilogueWarps * 32) : "memory");
             }
             ok = mbar_wait(tmem_full + 8 * acc, acc_ph, 6);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
+            if (!ok) *epi_abort = 1;
+            // the staged vectors are visible, and the give-up decision is the same for every epilogue warp
+            asm volatile("bar.sync 1, %0;" ::"n"(kNumEpilogueWarps * 32) : "memory");
+            if (*epi_abort) break;
             tc_fence_after();
             const uint32_t t_row = tmem_acc + ((uint32_t)(quad * 32) << 16) + acc * BN;
             if (SPLIT) {
@@ -455,9 +461,7 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             if (warp == kFirstEpilogueWarp && lane == 0) QB_TRACE(3);
             if (!SPLIT && FUSED && ep.n_peer > 0) {
                 // Hand the tile (now in the local output) to the push warps; at most two tiles may be pending.
-                ok = mbar_wait(push_free + 8 * acc, acc_ph ^ 1u, 11);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
+                if (!mbar_wait(push_free + 8 * acc, acc_ph ^ 1u, 11)) *epi_abort = 1;  // all warps leave at the next tile's barrier
                 __threadfence_block();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(out_ready + 8 * acc);
@@ -647,6 +651,7 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const uint32_t empty_a = full_a + 8 * A_STAGES;
     const uint32_t tmem_slot = empty_a + 8 * A_STAGES;
     volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - raw_base));
+    volatile int* epi_abort = reinterpret_cast<volatile int*>(smem_raw + (tmem_slot + 12 - raw_base));  // see gemm_i4_kernel
     // A8: packed B stages are compact (TN * 64 bytes each), which leaves room for a third A slot behind them
     constexpr int PB_BYTES = A8 ? TN * PK_ROW : P_BYTES;
     auto a_slot = [&](uint32_t sa) { return sa < 2 ? u_base + sa * U_BYTES : p_base + P_STAGES * (TN * PK_ROW); };
@@ -680,6 +685,7 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             mbar_init(push_free + 8 * i, kPushWarps);
         }
         fence_barrier_init();
+        *epi_abort = 0;
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, 512);
@@ -696,7 +702,7 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             if (!A8) tma_prefetch_desc(&tmap_a);
             tma_prefetch_desc(&tmap_b);
             uint32_t it = 0;
-            bool ok = true;
+            bool ok = ep.test_skip_producer == 0;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 const int m0 = (tile % tiles_m) * TM;
                 const int n0 = (tile / tiles_m) * TN;
@@ -783,11 +789,11 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     a_add = ep.a_add[row];
                     half_a_mul = 0.5f * bf16_to_f32(ep.a_mul[row]);
                 }
-                asm volatile("bar.sync 1, %0;" ::"n"(kEpiWarps * 32) : "memory");
             }
             ok = mbar_wait(tmem_full, local_tile & 1u, 6);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
+            if (!ok) *epi_abort = 1;
+            asm volatile("bar.sync 2, %0;" ::"n"(kEpiWarps * 32) : "memory");  // vectors staged; uniform give-up decision
+            if (*epi_abort) break;
             tc_fence_after();
             const uint32_t t_row = tmem_acc + ((uint32_t)(quad * 32) << 16) + half * TN;
             if (m0 + half * 128 < M) {  // warp-uniform: otherwise this accumulator was not computed
@@ -809,16 +815,14 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             if (lane == 0) mbar_arrive(tmem_empty);
             if (warp == kFirstEpi && lane == 0) QB_TRACE(3);
             if (PUSH) {
-                ok = mbar_wait(push_free + 8 * slot, slot_ph ^ 1u, 11);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
+                if (!mbar_wait(push_free + 8 * slot, slot_ph ^ 1u, 11)) *epi_abort = 1;  // all warps leave at the next tile's barrier
                 __threadfence_block();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(out_ready + 8 * slot);
                 if (tile + (int)gridDim.x >= num_tiles) {  // last tile: wait until all of it is in the local output, then help
                     ok = mbar_wait(out_ready + 8 * slot, slot_ph, 18);
                     ok = __all_sync(0xffffffffu, ok);
-                    if (!ok) break;
+                    if (!ok) break;  // no named barrier follows the last tile
                     push_tile_rows(ep, m0, n0, min(TM, M - m0), min(TN, N - n0), kPushWarps + (warp - kFirstEpi),
                                    kPushWarps + kEpiWarps, lane);
                 }
@@ -976,47 +980,52 @@ static int launch_gemm(const EpilogueParams& ep, const void* a, const void* b, i
 
 // ---- split-K scratch --------------------------------------------------------------------------------------------
 // Split-K needs a rows x 256 int32 slab per work item (tile, K range) and one counter per output tile; the counters are
-// zero between launches (the kernel leaves them so), the slabs need no initialisation.  The ordinary entry points keep one such buffer per device, allocated (and zeroed) on first use and grown on
-// demand - never while the stream is being captured into a graph, where the launch falls back to the kernel without
-// split-K.  One split-K launch per device may be in flight at a time (launches on one stream are).
+// zero between launches (the kernel leaves them so; reset_split_counters() restores that after a kernel reported a
+// timeout), the slabs need no initialisation.  The ordinary entry points keep ONE such buffer per device.  It has a
+// fixed size - kSplitSlabs slabs of 128 x 256 int32 (21 MB) and kSplitTiles counters, enough for every split the
+// library chooses itself (tiles x ranges <= number of SMs) - is allocated on the first launch that wants it and is
+// never freed, grown or moved afterwards: a CUDA graph that captured a split-K launch keeps valid pointers for the
+// life of the process.  It is not allocated while the stream is being captured; a request that does not fit (only a
+// forced split count can ask for that) or cannot be served runs the kernels without split-K instead.  One split-K
+// launch per device may be in flight at a time (launches on one stream are).
 struct SplitScratch {
     int32_t* sums = nullptr;
     int* counters = nullptr;
     size_t ints = 0;
     int tiles = 0;
 };
+constexpr size_t kSplitSlabs = 160;
+constexpr size_t kSplitInts = kSplitSlabs * 128 * 256;
+constexpr int kSplitTiles = 4096;
 static SplitScratch g_split_scratch[64];
 static std::mutex g_split_mutex;
 
 static bool get_split_scratch(int dev, cudaStream_t stream, size_t need_ints, int need_tiles, SplitScratch* out) {
     if (dev < 0 || dev >= 64) return false;
+    if (need_ints > kSplitInts || need_tiles > kSplitTiles) return false;
     std::lock_guard<std::mutex> lock(g_split_mutex);
     SplitScratch& ws = g_split_scratch[dev];
-    if (ws.ints < need_ints || ws.tiles < need_tiles) {
+    if (ws.sums == nullptr) {
         cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
         if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
             cudaGetLastError();
             return false;
         }
-        if (cudaDeviceSynchronize() != cudaSuccess) return false;  // nothing may still use the old buffer
-        if (ws.sums) cudaFree(ws.sums);
-        ws = SplitScratch{};
-        const size_t ints = need_ints > (size_t)2 << 20 ? need_ints : (size_t)2 << 20;
-        const int tiles = need_tiles > 1024 ? need_tiles : 1024;
         void* ptr = nullptr;
-        if (cudaMalloc(&ptr, (ints + (size_t)tiles) * sizeof(int)) != cudaSuccess) {
+        if (cudaMalloc(&ptr, (kSplitInts + (size_t)kSplitTiles) * sizeof(int)) != cudaSuccess) {
             cudaGetLastError();
             return false;
         }
-        if (cudaMemset(ptr, 0, (ints + (size_t)tiles) * sizeof(int)) != cudaSuccess) {
+        int* counters = reinterpret_cast<int*>(static_cast<int32_t*>(ptr) + kSplitInts);
+        if (cudaMemset(counters, 0, (size_t)kSplitTiles * sizeof(int)) != cudaSuccess) {  // synchronous: done before any launch
             cudaFree(ptr);
             cudaGetLastError();
             return false;
         }
         ws.sums = static_cast<int32_t*>(ptr);
-        ws.counters = reinterpret_cast<int*>(ws.sums + ints);
-        ws.ints = ints;
-        ws.tiles = tiles;
+        ws.counters = counters;
+        ws.ints = kSplitInts;
+        ws.tiles = kSplitTiles;
     }
     *out = ws;
     return true;
@@ -1046,6 +1055,23 @@ static bool get_static_scratch(int dev, SplitScratch* out) {
     out->ints = kStaticScratchInts;
     out->tiles = kStaticScratchTiles;
     return true;
+}
+
+// Zeroes the tile counters of both scratch buffers of the current device.  A launch that ended through a bounded-wait
+// timeout may have left counters half way; without this every later split-K launch on the device would complete its
+// tiles too early or never.  Called (after a device synchronisation) when a non-zero device status is fetched.
+static void reset_split_counters() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return;
+    int* allocated = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_split_mutex);
+        allocated = g_split_scratch[dev].counters;
+    }
+    if (allocated != nullptr) cudaMemset(allocated, 0, (size_t)kSplitTiles * sizeof(int));
+    SplitScratch st;
+    if (get_static_scratch(dev, &st)) cudaMemset(st.counters, 0, (size_t)kStaticScratchTiles * sizeof(int));
+    cudaGetLastError();
 }
 
 // Number of K ranges for the 128 x 256 kernel, or 1.  Split-K pays when the output has so few tiles that most SMs
@@ -1223,6 +1249,15 @@ static int run_gemm(bool fused, const EpilogueParams& ep_in, const void* a, cons
         const int tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);
         const int slab_rows = M >= BM ? BM : (M + 7) / 8 * 8;
         ep.slab_ints = slab_rows * 256;
+        if (static_splits == 0) {
+            // The library's own choice must never be refused: use as many K ranges as the static array holds
+            // (down to 1 = the kernels without scratch).  Only an explicit request (static_splits >= 2) can fail.
+            while (splits >= 2 && ((size_t)tiles * splits * ep.slab_ints > kStaticScratchInts || tiles > kStaticScratchTiles))
+                --splits;
+        }
+    }
+    if (splits >= 2) {
+        const int tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);
         const size_t need = (size_t)tiles * splits * ep.slab_ints;
         SplitScratch ws;
         bool have;
@@ -1367,6 +1402,29 @@ extern "C" int fused_matmul_dequantize_int4_int4t_bf16_cuda(void* mat_d, const v
                                                                 vec_a_mul, vec_b_mul, M, K, N, stream);
 }
 
+extern "C" int quest_b200_test_bounded_wait_cuda(void* mat_d, const void* mat_a, const void* mat_b, const void* vec_a_add,
+                                                 const void* vec_b_add, const void* vec_a_mul, const void* vec_b_mul, int M,
+                                                 int K, int N, long long wait_limit_cycles, cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || K <= 0 || !vec_a_add || !vec_b_add || !vec_a_mul || !vec_b_mul) return QB200_ERR_INVALID_ARGUMENT;
+    if (wait_limit_cycles <= 0 || wait_limit_cycles > kWaitLimitCycles) return QB200_ERR_INVALID_ARGUMENT;
+    if (cudaDeviceSynchronize() != cudaSuccess) return QB200_ERR_CUDA;
+    int st = set_wait_limit_cycles(wait_limit_cycles);
+    if (st != QB200_OK) return st;
+    EpilogueParams ep{};
+    ep.out = mat_d;
+    ep.ld = N;
+    ep.a_add = static_cast<const int32_t*>(vec_a_add);
+    ep.b_add = static_cast<const int32_t*>(vec_b_add);
+    ep.a_mul = static_cast<const __nv_bfloat16*>(vec_a_mul);
+    ep.b_mul = static_cast<const __nv_bfloat16*>(vec_b_mul);
+    ep.test_skip_producer = 1;
+    st = run_gemm(true, ep, mat_a, mat_b, M, K, N, stream, /*static_splits=*/1);  // tensor-core kernels, no split-K, no dp4a kernel
+    const bool synced = cudaStreamSynchronize(stream) == cudaSuccess;
+    const int st2 = set_wait_limit_cycles(kWaitLimitCycles);
+    if (st != QB200_OK) return st;
+    return synced ? st2 : QB200_ERR_CUDA;
+}
+
 extern "C" int quest_b200_device_status(int* status) {
     if (status == nullptr) return QB200_ERR_INVALID_ARGUMENT;
     if (cudaDeviceSynchronize() != cudaSuccess) return QB200_ERR_CUDA;
@@ -1375,6 +1433,7 @@ extern "C" int quest_b200_device_status(int* status) {
     if (st != QB200_OK) return st;
     st = hq_tc_fetch_and_clear_device_status(&v2);  // the tensor-core quantiser keeps its own status word
     if (st != QB200_OK) return st;
+    if (v != 0) reset_split_counters();  // a GEMM that gave up may have left split-K tile counters half way
     *status = v != 0 ? v : v2;
     return QB200_OK;
 }

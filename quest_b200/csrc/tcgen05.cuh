@@ -51,14 +51,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Bounded wait: gives up after about a second of polling, records the failure and tells the caller.
+// Bounded wait: gives up after about a second of polling, records the failure and tells the caller.  The limit is a
+// device variable (one per translation unit) so that a test can shorten it to milliseconds; it is read only on the slow
+// path, after the first poll has failed.
 constexpr long long kWaitLimitCycles = 2000000000LL;
+static __device__ long long g_wait_limit_cycles = kWaitLimitCycles;
+
+static inline int set_wait_limit_cycles(long long cycles) {
+    if (cycles <= 0) cycles = kWaitLimitCycles;
+    return cudaMemcpyToSymbol(g_wait_limit_cycles, &cycles, sizeof(cycles)) == cudaSuccess ? QB200_OK : QB200_ERR_CUDA;
+}
+
 static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, int where) {
     const long long t0 = clock64();
+    const long long limit = *reinterpret_cast<volatile long long*>(&g_wait_limit_cycles);
     while (true) {
         for (int i = 0; i < 64; ++i)
             if (mbar_try_wait(bar, parity)) return true;
-        if (clock64() - t0 > kWaitLimitCycles) {
+        if (clock64() - t0 > limit) {
             atomicCAS(&g_device_status, 0, (where << 8) | QB200_ERR_DEVICE_TIMEOUT);
             return false;
         }

@@ -45,6 +45,38 @@ def preprocess_weight(
     return w_int_packed, w_scale, w_add, None
 
 
+def fused_matmul_dequantize_int4_bf16(
+        mat_a: torch.Tensor,
+        mat_b: torch.Tensor,
+        vec_a_add: torch.Tensor,
+        vec_b_add: torch.Tensor,
+        vec_a_mul: torch.Tensor,
+        vec_b_mul: torch.Tensor,
+        mat_d: torch.Tensor,
+        _mat_c: torch.Tensor = None,
+        debug_mode: bool = True,
+) -> torch.Tensor:
+    """mat_d (M, N) bf16 = (2 * mat_a @ mat_b^T + vec_a_add + vec_b_add^T) * (.5 * vec_a_mul * vec_b_mul^T).
+
+    The switch of gemm-quest/benchmarks/utils.py:548-587: ``debug_mode=True`` (the reference's default) takes the
+    unfused route - int32 GEMM into ``_mat_c`` (allocated if absent), then ``add_mul_vv`` - and ``debug_mode=False``
+    the fused kernel.  Here both routes evaluate the same exact expression, so their results are bit-identical.
+    ``mat_d`` may be None (allocated in the dtype of ``vec_a_mul``)."""
+    M, N = mat_a.size(0), mat_b.size(0)
+    device = mat_a.device
+    if mat_d is None:
+        mat_d = torch.empty(M, N, dtype=vec_a_mul.dtype, device=device)
+    if debug_mode:
+        mat_c = torch.empty(M, N, dtype=torch.int32, device=device) if _mat_c is None else _mat_c
+        quest.matmul_int4_int4t_int32(mat_a=mat_a, mat_b=mat_b, out=mat_c)
+        quest.add_mul_vv(vec_a_add=vec_a_add, vec_a_mul=vec_a_mul, vec_b_add=vec_b_add, vec_b_mul=vec_b_mul,
+                         mat_c=mat_c, mat_d=mat_d)
+    else:
+        quest.fused_matmul_dequantize_int4_int4t_bf16(mat_a=mat_a, mat_b=mat_b, vec_a_add=vec_a_add, vec_b_add=vec_b_add,
+                                                      vec_a_mul=vec_a_mul, vec_b_mul=vec_b_mul, out=mat_d)
+    return mat_d
+
+
 def linear_forward(
         activation: torch.Tensor,
         w_int_packed: torch.Tensor,
@@ -60,10 +92,12 @@ def linear_forward(
         backend: str = 'cuda',
         block: int = HADAMARD_BLOCK,
         _a_int8: torch.Tensor = None,
+        debug_mode: bool = False,
 ) -> torch.Tensor:
     """out (M, N) bf16 = activation (M, K) @ weight^T in W4A4.  The ``_a_*`` arguments are optional
-    caller-owned workspaces (CUDA-graph friendly), as in the reference.  ``_c``, if given, makes the
-    call take the unfused int32 GEMM + add_mul_vv route (the reference's debug mode).
+    caller-owned workspaces (CUDA-graph friendly), as in the reference.  As in the reference (utils.py:100) the
+    fused kernel is used whether or not ``_c`` is given; ``debug_mode=True`` (not in the reference's signature)
+    takes the unfused int32 GEMM + add_mul_vv route with ``_c`` as its int32 workspace.
 
     With ``use_hadamard`` and a shape for which the library prefers it, the quantiser writes the GEMM's int8 operand
     directly (``_a_int8`` [M, K] uint8 is its workspace) instead of packed int4: same codes, same result, no unpack
@@ -76,7 +110,7 @@ def linear_forward(
         out = torch.empty(M, N, dtype=dtype, device=device)
     a_scale = torch.empty(M, 1, dtype=dtype, device=device) if _a_scale is None else _a_scale
     a_int_row_sum = torch.empty(M, 1, dtype=torch.int32, device=device) if _a_int_row_sum is None else _a_int_row_sum
-    if (use_hadamard and _c is None and (_a_int8 is not None or _a_int_packed is None) and K % block == 0
+    if (use_hadamard and not debug_mode and (_a_int8 is not None or _a_int_packed is None) and K % block == 0
             and quest.prefers_a8(M, K, N)):
         a_int8 = torch.empty(M, K, dtype=torch.uint8, device=device) if _a_int8 is None else _a_int8
         quest.hadamard_quantize_a8(activation, block=block, x_a8=a_int8, scale=a_scale, x_int_row_sum=a_int_row_sum)
@@ -91,14 +125,8 @@ def linear_forward(
         quest.find_scale_int4(x=activation, scale=a_scale)
         quest.quantize_int4(x=activation, scale=a_scale, x_int=None, x_int_packed=a_int_packed,
                             x_int_row_sum=a_int_row_sum, do_dequantize=False)
-    if _c is not None:
-        quest.matmul_int4_int4t_int32(mat_a=a_int_packed, mat_b=w_int_packed, out=_c)
-        quest.add_mul_vv(vec_a_add=a_int_row_sum, vec_a_mul=a_scale, vec_b_add=w_add, vec_b_mul=w_scale,
-                         mat_c=_c, mat_d=out)
-    else:
-        quest.fused_matmul_dequantize_int4_int4t_bf16(mat_a=a_int_packed, mat_b=w_int_packed,
-                                                      vec_a_add=a_int_row_sum, vec_b_add=w_add,
-                                                      vec_a_mul=a_scale, vec_b_mul=w_scale, out=out)
+    fused_matmul_dequantize_int4_bf16(mat_a=a_int_packed, mat_b=w_int_packed, vec_a_add=a_int_row_sum, vec_b_add=w_add,
+                                      vec_a_mul=a_scale, vec_b_mul=w_scale, mat_d=out, _mat_c=_c, debug_mode=debug_mode)
     return out
 
 

@@ -399,8 +399,12 @@ def test_linear_forward_matches_reference_golden(case):
     assert y.cpu().equal(gd["m"])
     # debug route (int32 GEMM + add_mul_vv) gives the same bits
     c = torch.empty(y.shape, dtype=torch.int32, device=DEV)
-    y2 = quest.linear_forward(gd["activation"].to(DEV), wp, ws, wa, use_hadamard=False, _c=c)
+    y2 = quest.linear_forward(gd["activation"].to(DEV), wp, ws, wa, use_hadamard=False, _c=c, debug_mode=True)
     assert y2.equal(y) and c.cpu().equal(gd["c_ref"])
+    # as in the reference, a caller-provided _c alone does not leave the fused route (and is not written)
+    c.fill_(-7)
+    y3 = quest.linear_forward(gd["activation"].to(DEV), wp, ws, wa, use_hadamard=False, _c=c)
+    assert y3.equal(y) and int((c != -7).sum()) == 0
 
 
 def test_linear_forward_with_hadamard_config1():

@@ -1,0 +1,230 @@
+"""GPU parity at the sizes the benchmarks are quoted on: the down-projection row lengths (K = 5632, 11008) and the other
+7B / 70B row lengths for the fused Hadamard+quantise kernels, launches of 4096 and 65536 rows, and the int4 GEMM at the
+corners of the 7B sweep and on the column shards of the 70B layers.
+
+Small and medium cases are compared with the CPU oracle directly.  Where the oracle would need minutes (a full
+8192 x 12288 x 4096 product) the exact int32 accumulators are compared with cuBLAS int8 on the unpacked codes plus
+O(MK + NK) row/column checksums computed on the CPU, and the fused output with the oracle's epilogue expression
+evaluated on those exact accumulators."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+from oracle import quest_oracle as O
+from conftest import make_activations
+
+pytestmark = pytest.mark.gpu
+
+if torch.cuda.is_available():
+    import quest_b200 as quest
+    DEV = torch.device("cuda:0")
+
+
+@pytest.fixture(autouse=True)
+def _device_status_clean():
+    yield
+    assert quest.device_status() == 0, "a kernel reported a bounded-wait timeout"
+
+
+def hq_against_oracle(x: torch.Tensor, block: int, packed, scale, row_sum) -> tuple[int, int]:
+    """Codes / scales / row sums of the rows ``x`` (CPU) against the canonical oracle.  Returns (code flips, scale flips)."""
+    p_ref, s_ref, r_ref, _ = O.hadamard_quantize_int4(x, block)
+    packed, scale, row_sum = packed.cpu(), scale.cpu(), row_sum.cpu()
+    assert int(O.bf16_ulp_distance(scale, s_ref).max()) <= 1
+    same = (scale == s_ref).view(-1)
+    nflip, maxd = O.count_code_flips(packed[same], p_ref[same])
+    assert maxd <= 1
+    assert row_sum.equal(O.unpack_int4(packed).to(torch.int32).sum(-1, keepdim=True))
+    return nflip, int((~same).sum())
+
+
+# ------------------------------------------------------------------ Hadamard + quantise ----------------
+# K = 5632 (44 blocks) and 11008 (86 blocks) are the down-projection row lengths: the tcgen05 kernel's tiling refuses
+# them, so they run on hadamard_quant_mma_kernel; 10240 and 12288 are further 7B / 70B row lengths.
+@pytest.mark.parametrize("block", [64, 128, 256])
+@pytest.mark.parametrize("k", [5632, 11008, 10240, 12288])
+@pytest.mark.parametrize("kind,m", [("student", 1), ("laplace", 33), ("randn", 300)])
+@pytest.mark.parametrize("kernel", ["auto", "mma"])
+def test_hadamard_quantize_down_projection_row_lengths(block, k, kind, m, kernel, monkeypatch):
+    if kernel != "auto":
+        monkeypatch.setenv("QB200_HQ_KERNEL", kernel)
+    x = make_activations(kind, m, k, seed=block + m + k)
+    packed, scale, row_sum = quest.hadamard_quantize_int4(x.to(DEV), block)
+    nflip, sflip = hq_against_oracle(x, block, packed, scale, row_sum)
+    assert nflip <= 1 + int(5e-6 * m * k), (nflip, m * k)
+    assert sflip <= max(1, m // 1000)
+
+
+@pytest.mark.parametrize("k", [4096, 5632, 11008])
+def test_hadamard_quantize_4096_rows(k):
+    """A launch of 4096 tokens (the bandwidth sweep's middle size), every row against the oracle."""
+    m = 4096
+    x = make_activations("laplace", m, k, seed=k)
+    packed, scale, row_sum = quest.hadamard_quantize_int4(x.to(DEV), 128)
+    nflip, sflip = hq_against_oracle(x, 128, packed, scale, row_sum)
+    assert nflip <= 1 + int(5e-6 * m * k), (nflip, m * k)
+    assert sflip <= max(1, m // 1000)
+
+
+@pytest.mark.parametrize("k,block", [(4096, 128), (8192, 64), (14336, 256)])
+def test_hadamard_quantize_65536_rows_sampled(k, block):
+    """The largest launch of the bandwidth sweep (65536 tokens): 256 rows spread over the whole launch (first, last and
+    a fixed stride in between) against the oracle, and the row sums of every row against the codes written."""
+    m = 65536
+    g = torch.Generator(device=DEV).manual_seed(k)
+    x = torch.empty(m, k, dtype=torch.bfloat16, device=DEV)
+    for r0 in range(0, m, 8192):  # Laplace(0, 1) with every hundredth column x50, generated on the device in slabs
+        u = torch.rand(8192, k, generator=g, device=DEV) - 0.5
+        v = -u.sign() * torch.log1p(-2 * u.abs())
+        v[:, ::100] *= 50
+        x[r0:r0 + 8192] = v.to(torch.bfloat16)
+        del u, v
+    packed, scale, row_sum = quest.hadamard_quantize_int4(x, block)
+    rows = torch.cat([torch.arange(0, m, 257), torch.tensor([m - 1])])[:256].to(DEV)
+    nflip, sflip = hq_against_oracle(x[rows].cpu(), block, packed[rows], scale[rows], row_sum[rows])
+    assert nflip <= 1 + int(5e-6 * rows.numel() * k)
+    assert sflip <= 1
+    for r0 in range(0, m, 16384):
+        codes = quest.unpack_int4(packed[r0:r0 + 16384])
+        assert row_sum[r0:r0 + 16384].equal(codes.sum(-1, keepdim=True, dtype=torch.int32))
+        del codes
+
+
+def test_hadamard_quantize_real_down_projection_layer():
+    """The 800M model's down projection (K = 5632 -> N = 2048) at 1024 tokens, layer output against the oracle layer."""
+    m, k, n = 1024, 5632, 2048
+    x = make_activations("student", m, k, seed=3)
+    w = (0.02 * torch.randn(n, k, generator=torch.Generator().manual_seed(4))).to(torch.bfloat16)
+    wp, ws, wa, _ = O.preprocess_weight(w, use_hadamard=True)
+    y = quest.linear_forward(x.to(DEV), wp.to(DEV), ws.to(DEV), wa.to(DEV), use_hadamard=True).cpu()
+    y_ref = O.linear_forward(x, wp, ws, wa, use_hadamard=True)
+    pa, sa, _ = quest.hadamard_quantize_int4(x.to(DEV))
+    pa_ref, sa_ref, _, _ = O.hadamard_quantize_int4(x)
+    if pa.cpu().equal(pa_ref) and sa.cpu().equal(sa_ref):
+        assert y.equal(y_ref)
+    else:  # a tie flip of one activation code moves one row of outputs by at most a few ulp
+        assert (y != y_ref).float().mean() < 0.02
+        assert ((y.float() - y_ref.float()).norm() / y_ref.float().norm()).item() < 1e-3
+
+
+# ------------------------------------------------------------------ int4 GEMM at the benchmark shapes ---
+def random_packed_dev(rows: int, k: int, seed: int) -> torch.Tensor:
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, 256, (rows, k // 2), generator=g, dtype=torch.uint8).to(DEV)  # every byte = two uniform codes
+
+
+def epilogue_vectors(m: int, n: int, seed: int):
+    g = torch.Generator().manual_seed(seed)
+    a_add = torch.randint(-8 * 64, 8 * 64, (m, 1), generator=g, dtype=torch.int32)
+    b_add = torch.randint(-8 * 64, 8 * 64, (n, 1), generator=g, dtype=torch.int32)
+    a_mul = (torch.rand(m, 1, generator=g) + 0.05).to(torch.bfloat16)
+    b_mul = (0.02 * torch.rand(n, 1, generator=g) + 0.001).to(torch.bfloat16)
+    return [t.to(DEV) for t in (a_add, a_mul, b_add, b_mul)]
+
+
+def cublas_int8_product(ad: torch.Tensor, bd: torch.Tensor) -> torch.Tensor:
+    a8 = quest.unpack_int4(ad)
+    if a8.size(0) <= 16:  # torch._int_mm wants more than 16 rows
+        a8 = torch.cat([a8, torch.zeros(32 - a8.size(0), a8.size(1), dtype=torch.int8, device=DEV)])
+    return torch._int_mm(a8, quest.unpack_int4(bd).t().contiguous())[:ad.size(0)]
+
+
+BENCH_GEMM_SHAPES = [
+    # corners of the 7B sweep (K = 4096)
+    (8192, 4096, 12288), (128, 4096, 11008), (2048, 4096, 11008), (8192, 4096, 4096), (1, 4096, 12288), (16, 4096, 11008),
+    # column shards of the 70B layers: K = 8192 with N/g in {3584, 1280}, K = 28672 with N/g = 1024
+    (16, 8192, 3584), (2048, 8192, 3584), (16, 8192, 1280), (2048, 8192, 1280), (16, 28672, 1024), (2048, 28672, 1024),
+]
+
+
+@pytest.mark.parametrize("m,k,n", BENCH_GEMM_SHAPES)
+def test_gemm_benchmark_shapes_exact(m, k, n):
+    ad, bd = random_packed_dev(m, k, m + k), random_packed_dev(n, k, n + k + 1)
+    c = quest.matmul_int4_int4t_int32(ad, bd)
+    ref = cublas_int8_product(ad, bd)
+    assert c.equal(ref)
+    # checksums against CPU arithmetic that never forms the product: sum_n C[m, n] = A[m, :] . (sum_n B[n, :])
+    ai, bi = O.unpack_int4(ad.cpu()).to(torch.int64), O.unpack_int4(bd.cpu()).to(torch.int64)
+    assert c.sum(dim=1, dtype=torch.int64).cpu().equal(ai @ bi.sum(dim=0))
+    assert c.sum(dim=0, dtype=torch.int64).cpu().equal(bi @ ai.sum(dim=0))
+    # fused output = the oracle's epilogue expression on those exact accumulators
+    a_add, a_mul, b_add, b_mul = epilogue_vectors(m, n, m + n)
+    want = O.add_mul_vv(a_add, a_mul, b_add, b_mul, ref, torch.empty(m, n, dtype=torch.bfloat16, device=DEV))
+    got = quest.fused_matmul_dequantize_int4_int4t_bf16(ad, bd, a_add, b_add, a_mul, b_mul)
+    assert got.equal(want)
+    if m <= 256:  # small enough for the CPU oracle end to end
+        cpu = O.fused_matmul_dequantize_int4_int4t_bf16(ad.cpu(), bd.cpu(), a_add.cpu(), b_add.cpu(), a_mul.cpu(), b_mul.cpu())
+        assert got.cpu().equal(cpu)
+
+
+def test_fused_matmul_dequantize_int4_bf16_switch():
+    """The Python switch of the reference's layer code: debug_mode=True (int32 GEMM + add_mul_vv, with and without a
+    caller-owned int32 workspace) and debug_mode=False (fused kernel) give the oracle's bits."""
+    m, k, n = 160, 768, 224
+    ad, bd = random_packed_dev(m, k, 1), random_packed_dev(n, k, 2)
+    a_add, a_mul, b_add, b_mul = epilogue_vectors(m, n, 3)
+    ref = O.fused_matmul_dequantize_int4_int4t_bf16(ad.cpu(), bd.cpu(), a_add.cpu(), b_add.cpu(), a_mul.cpu(), b_mul.cpu())
+    d = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    c = torch.empty(m, n, dtype=torch.int32, device=DEV)
+    out = quest.fused_matmul_dequantize_int4_bf16(ad, bd, a_add, b_add, a_mul, b_mul, d, _mat_c=c, debug_mode=True)
+    assert out is d and d.cpu().equal(ref) and c.cpu().equal(O.matmul_int4_int4t_int32(ad.cpu(), bd.cpu()))
+    out = quest.fused_matmul_dequantize_int4_bf16(ad, bd, a_add, b_add, a_mul, b_mul, None)  # the reference's default: debug
+    assert out.dtype == torch.bfloat16 and out.cpu().equal(ref)
+    d.zero_()
+    quest.fused_matmul_dequantize_int4_bf16(ad, bd, a_add, b_add, a_mul, b_mul, d, debug_mode=False)
+    assert d.cpu().equal(ref)
+
+
+def test_split_k_graph_survives_a_larger_eager_request(monkeypatch):
+    """A CUDA graph that captured a split-K launch keeps working after an eager call that needs far more split-K scratch:
+    the per-device scratch buffer has a fixed size and is never freed or moved."""
+    m, k, n = 16, 8192, 1024
+    ad, bd = random_packed_dev(m, k, 5), random_packed_dev(n, k, 6)
+    out = torch.zeros(m, n, dtype=torch.int32, device=DEV)
+    ref = cublas_int8_product(ad, bd)
+    monkeypatch.setenv("QB200_GEMM_SPLITS", "8")
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        for _ in range(2):
+            quest.matmul_int4_int4t_int32(ad, bd, out=out)  # allocates the scratch outside the capture
+    torch.cuda.current_stream().wait_stream(s)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        quest.matmul_int4_int4t_int32(ad, bd, out=out)
+    # 16 tiles x 8 ranges x 96 rows: six times the slabs of the captured launch
+    big_a, big_b = random_packed_dev(96, 16384, 7), random_packed_dev(4096, 16384, 8)
+    big = quest.matmul_int4_int4t_int32(big_a, big_b)
+    assert big.equal(cublas_int8_product(big_a, big_b))
+    out.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert out.equal(ref)
+
+
+def test_bounded_wait_runs_out_and_is_reported(monkeypatch):
+    """A launch whose TMA producer issues nothing: every consumer wait runs out after the shortened limit, the kernel
+    returns, the status word names a wait site of the GEMM, and the next ordinary call is exact with a clean status."""
+    from quest_b200 import _lib
+    m, k, n = 300, 1024, 520
+    ad, bd = random_packed_dev(m, k, 9), random_packed_dev(n, k, 10)
+    a_add, a_mul, b_add, b_mul = epilogue_vectors(m, n, 11)
+    d = torch.zeros(m, n, dtype=torch.bfloat16, device=DEV)
+    want = O.fused_matmul_dequantize_int4_int4t_bf16(ad.cpu(), bd.cpu(), a_add.cpu(), b_add.cpu(), a_mul.cpu(), b_mul.cpu())
+    lib = _lib.load()
+    for tile in ("128", "512"):  # the 128-row kernel and the 256 x 256 kernel
+        monkeypatch.setenv("QB200_GEMM_TILE", tile)
+        st = lib.quest_b200_test_bounded_wait_cuda(d.data_ptr(), ad.data_ptr(), bd.data_ptr(), a_add.data_ptr(),
+                                                   b_add.data_ptr(), a_mul.data_ptr(), b_mul.data_ptr(), m, k, n,
+                                                   4_000_000, torch.cuda.current_stream().cuda_stream)
+        monkeypatch.delenv("QB200_GEMM_TILE")
+        assert st == 0
+        status = quest.device_status()
+        assert status & 0xFF == 5, hex(status)            # QB200_ERR_DEVICE_TIMEOUT
+        assert (status >> 8) in (4, 6, 7, 8), hex(status)  # MMA issuer, epilogue or unpack warps waiting for data
+        assert quest.device_status() == 0                  # reading it cleared it
+        assert float(d.abs().max()) == 0.0                 # nothing was written
+        got = quest.fused_matmul_dequantize_int4_int4t_bf16(ad, bd, a_add, b_add, a_mul, b_mul)
+        assert got.cpu().equal(want)
+        assert quest.device_status() == 0

@@ -26,8 +26,10 @@ def _inputs(m, k, n, seed):
     return a, b, a_add, b_add, a_mul, b_mul
 
 
+# (128, 65536, 2048) and (96, 16384, 4096) with splits = 0: the library's usual choice of K ranges would need more than
+# the static array holds, so it must take fewer ranges rather than refuse.
 @pytest.mark.parametrize("m,k,n,splits", [(16, 4096, 4096, 0), (1, 2048, 1024, 4), (40, 1024, 520, 3), (128, 512, 256, 2),
-                                          (300, 512, 264, 0)])
+                                          (300, 512, 264, 0), (128, 65536, 2048, 0), (96, 16384, 4096, 0)])
 def test_noalloc_entry_point_matches_the_ordinary_one_twice(m, k, n, splits):
     host = _inputs(m, k, n, seed=m + n)
     a, b, a_add, b_add, a_mul, b_mul = (t.to(DEV) for t in host)

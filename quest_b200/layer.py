@@ -13,6 +13,7 @@ import torch
 from torch import nn
 
 import quest_b200 as quest
+from .workspace import default_cache
 
 HADAMARD_BLOCK = 128  # the reference hard-codes block 128 (utils.py:17, 39, 90)
 
@@ -150,6 +151,7 @@ class Linear4bit(nn.Module):
         self.in_features, self.out_features = in_features, out_features
         self.use_hadamard: bool = use_hadamard
         self.use_noop: bool = use_noop
+        self.workspaces = default_cache  # a WorkspaceCache; replace it to give a module (or a model) its own
         nn_linear = nn.Linear(in_features, out_features, bias=bias, device=device, dtype=dtype)
         if weight is not None:
             nn_linear.weight.data.copy_(weight)
@@ -166,8 +168,12 @@ class Linear4bit(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if not self.use_noop:
             a = x.contiguous().flatten(end_dim=-2)
+            # activation-side workspaces come from the shared per-stream cache: nothing but the output is allocated
+            m, k = a.shape
+            a8 = self.use_hadamard and k % HADAMARD_BLOCK == 0 and quest.prefers_a8(m, k, self.out_features)
+            ws = self.workspaces.get(m, k, a.device, a.dtype, int8_operand=a8)
             y = linear_forward(activation=a, w_int_packed=self.w_int_packed, w_scale=self.w_scale, w_add=self.w_add,
-                               w_meta_e=self.w_meta_e, out=None, use_hadamard=self.use_hadamard)
+                               w_meta_e=self.w_meta_e, out=None, use_hadamard=self.use_hadamard, **ws)
             y = y.unflatten(dim=0, sizes=x.shape[:-1])
         else:
             if self.use_hadamard:

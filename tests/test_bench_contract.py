@@ -24,6 +24,13 @@ def test_reference_arm_prints_one_json_line_with_the_contract_keys():
     assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
     assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["d2h_bytes_per_step"] == 0
     assert "workload" in line["config"]
+    assert line["steps"] == 2 and line["warmup"] == 1  # --steps / --warmup are honoured
+    # both arms of one command line carry the same `config` object
+    sys.path.insert(0, ROOT)
+    import argparse
+    import bench
+    args = argparse.Namespace(workload="linear", m=64, k=256, n=64, block=128, exchange="push")
+    assert line["config"] == bench.workload_config(args, 1)
 
 
 def test_other_ranks_of_the_reference_arm_exit_quietly():

@@ -585,7 +585,7 @@ constexpr int kWarps = kFirstPush + kPushWarps;
 constexpr int kThreads = kWarps * 32;
 constexpr int VEC_BYTES = TN * 8;
 constexpr int A_STAGES = 3;  // A8 variant: ring of the int8 A tiles (two in the A halves of the int8 stages, one behind the packed B ring)
-constexpr int NUM_BARS = 2 * P_STAGES + 2 * U_STAGES + 2 + 1 + 4 + 2 * A_STAGES;
+constexpr int NUM_BARS = 2 * P_STAGES + 2 * U_STAGES + 2 + 1 + 4 + 2 * A_STAGES + 1;
 constexpr int LAYOUT_BYTES = U_STAGES * U_BYTES + P_STAGES * P_BYTES + VEC_BYTES + NUM_BARS * 8 + 16;
 constexpr int SMEM_BYTES = 232448;  // all the shared memory one CTA can have; the layout needs a 1024-byte aligned start
 static_assert(LAYOUT_BYTES <= SMEM_BYTES, "layout does not fit");
@@ -649,7 +649,8 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const uint32_t push_free = out_ready + 16;  // [2]
     const uint32_t full_a = push_free + 16;      // [A_STAGES] A8 only
     const uint32_t empty_a = full_a + 8 * A_STAGES;
-    const uint32_t tmem_slot = empty_a + 8 * A_STAGES;
+    const uint32_t vec_ready = empty_a + 8 * A_STAGES;  // epilogue warps -> unpack warps: this tile's column vectors are staged
+    const uint32_t tmem_slot = vec_ready + 8;
     volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - raw_base));
     volatile int* epi_abort = reinterpret_cast<volatile int*>(smem_raw + (tmem_slot + 12 - raw_base));  // see gemm_i4_kernel
     // A8: packed B stages are compact (TN * 64 bytes each), which leaves room for a third A slot behind them
@@ -662,6 +663,12 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const int tiles_n = (N + TN - 1) / TN;
     const int num_tiles = tiles_m * tiles_n;
     const int num_kb = (K + BK - 1) / BK;
+    // The CTA's last tile: with nothing left to unpack, the unpack warps convert and store half of its columns.  Needs at
+    // least four K stages, so that a wait on the tile's barriers by parity cannot be answered by an older phase.
+    const int last_tile = (int)blockIdx.x < num_tiles
+                              ? (int)blockIdx.x + ((num_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x) * (int)gridDim.x : -1;
+    const bool help_last = !PUSH && num_kb >= 4;
+    uint32_t pre_issued = 0;  // producer thread: copies already issued before the CTA-wide synchronisation
 
     if (threadIdx.x == 0) {
         QB_TRACE(0);
@@ -680,12 +687,27 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         mbar_init(tmem_full, 1);
         mbar_init(tmem_empty, kEpiWarps);
         mbar_init(mma_done, 1);
+        mbar_init(vec_ready, kEpiWarps);
         for (int i = 0; i < 2; ++i) {
             mbar_init(out_ready + 8 * i, kEpiWarps);
             mbar_init(push_free + 8 * i, kPushWarps);
         }
         fence_barrier_init();
         *epi_abort = 0;
+        // The first copies of the CTA's first tile leave before tensor memory is allocated and the CTA has synchronised:
+        // they need nothing but the barriers initialised above (this thread is also the producer thread below).
+        if (ep.test_skip_producer == 0 && (int)blockIdx.x < num_tiles) {
+            if (!A8) tma_prefetch_desc(&tmap_a);
+            tma_prefetch_desc(&tmap_b);
+            const int m0 = ((int)blockIdx.x % tiles_m) * TM;
+            const int n0 = ((int)blockIdx.x / tiles_m) * TN;
+            for (; pre_issued < (uint32_t)P_STAGES && (int)pre_issued < num_kb; ++pre_issued) {
+                mbar_arrive_expect_tx(full_p + 8 * pre_issued, PB_BYTES);
+                const uint32_t dst = p_base + pre_issued * PB_BYTES;
+                if (!A8) tma_load_2d(dst, &tmap_a, (int)pre_issued * PK_ROW, m0, full_p + 8 * pre_issued);
+                tma_load_2d(A8 ? dst : dst + TM * PK_ROW, &tmap_b, (int)pre_issued * PK_ROW, n0, full_p + 8 * pre_issued);
+            }
+        }
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, 512);
@@ -699,14 +721,13 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
-            if (!A8) tma_prefetch_desc(&tmap_a);
-            tma_prefetch_desc(&tmap_b);
             uint32_t it = 0;
             bool ok = ep.test_skip_producer == 0;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 const int m0 = (tile % tiles_m) * TM;
                 const int n0 = (tile / tiles_m) * TN;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    if (it < pre_issued) continue;  // left before the CTA synchronised
                     const uint32_t s = it % P_STAGES, ph = (it / P_STAGES) & 1u;
                     if (!(ok = mbar_wait(empty_p + 8 * s, ph ^ 1u, 1))) break;
                     mbar_arrive_expect_tx(full_p + 8 * s, PB_BYTES);
@@ -790,15 +811,20 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     half_a_mul = 0.5f * bf16_to_f32(ep.a_mul[row]);
                 }
             }
+            if (FUSED) {  // tell the unpack warps (which help with the CTA's last tile) that this warp's share is staged
+                __syncwarp();
+                if (lane == 0) mbar_arrive(vec_ready);
+            }
             ok = mbar_wait(tmem_full, local_tile & 1u, 6);
             if (!ok) *epi_abort = 1;
             asm volatile("bar.sync 2, %0;" ::"n"(kEpiWarps * 32) : "memory");  // vectors staged; uniform give-up decision
             if (*epi_abort) break;
             tc_fence_after();
             const uint32_t t_row = tmem_acc + ((uint32_t)(quad * 32) << 16) + half * TN;
+            const int c_end = (help_last && tile == last_tile) ? TN / 2 : TN;  // the unpack warps take the other half
             if (m0 + half * 128 < M) {  // warp-uniform: otherwise this accumulator was not computed
 #pragma unroll 1
-                for (int c0 = 0; c0 < TN; c0 += 64) {
+                for (int c0 = 0; c0 < c_end; c0 += 64) {
                     if (n0 + c0 >= N) break;
                     uint32_t r0[32], r1[32];
                     tmem_ld32(t_row + c0, r0);
@@ -910,6 +936,46 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 if (lane == 0) {
                     mbar_arrive(full_u + 8 * us);
                     mbar_arrive(empty_p + 8 * ps);
+                }
+            }
+        }
+        // Nothing is left to unpack: convert and store columns TN/2 .. TN-1 of the CTA's last tile while the epilogue warps
+        // handle the first half.  Warp u of the unpack group stands beside epilogue warp u: same accumulator (u >> 2), and
+        // the tensor-memory lane quadrant its own warp index allows.
+        if (help_last && ok && last_tile >= 0) {
+            const uint32_t lt = (uint32_t)((last_tile - (int)blockIdx.x) / (int)gridDim.x);  // how many tiles came before it
+            const int m0 = (last_tile % tiles_m) * TM;
+            const int n0 = (last_tile / tiles_m) * TN;
+            const int quad = warp & 3;
+            const int half = (warp - kFirstUnpack) >> 2;
+            const int row = m0 + half * 128 + quad * 32 + lane;
+            const bool row_ok = row < M;
+            int a_add = 0;
+            float half_a_mul = 0.f;
+            if (FUSED && row_ok) {
+                a_add = ep.a_add[row];
+                half_a_mul = 0.5f * bf16_to_f32(ep.a_mul[row]);
+            }
+            const uint8_t* vec_ptr = smem_raw + (vec_base - raw_base);
+            const int* sb_add = reinterpret_cast<const int*>(vec_ptr);
+            const float* sb_mul = reinterpret_cast<const float*>(vec_ptr + TN * 4);
+            if (FUSED) ok = mbar_wait(vec_ready, lt & 1u, 22);
+            ok = ok && mbar_wait(tmem_full, lt & 1u, 23);
+            ok = __all_sync(0xffffffffu, ok);
+            if (ok && m0 + half * 128 < M) {
+                tc_fence_after();
+                const uint32_t t_row = tmem_acc + ((uint32_t)(quad * 32) << 16) + half * TN;
+#pragma unroll 1
+                for (int c0 = TN / 2; c0 < TN; c0 += 64) {
+                    if (n0 + c0 >= N) break;
+                    uint32_t r0[32], r1[32];
+                    tmem_ld32(t_row + c0, r0);
+                    tmem_ld32(t_row + c0 + 32, r1);
+                    tmem_ld_wait();
+                    if (!row_ok) continue;
+                    epilogue_store_chunk<FUSED>(r0, ep, row, n0 + c0, N, a_add, half_a_mul, sb_add + c0, sb_mul + c0);
+                    if (n0 + c0 + 32 < N)
+                        epilogue_store_chunk<FUSED>(r1, ep, row, n0 + c0 + 32, N, a_add, half_a_mul, sb_add + c0 + 32, sb_mul + c0 + 32);
                 }
             }
         }

@@ -52,7 +52,7 @@ int quest_b200_device_status(int* status);
 
 /*
  * Test support: launches the fused GEMM with its TMA producer switched off and the limit of every bounded in-kernel
- * wait shortened to wait_limit_cycles (SM clock cycles; a few million = a few milliseconds), so that the waits of the
+ * wait shortened to wait_limit_cycles (SM clock cycles, at least one million; a few million = a few milliseconds), so that the waits of the
  * consumer warps run out by construction - no trap, no fault, no unbounded spin.  The kernel records
  * QB200_ERR_DEVICE_TIMEOUT, releases what it holds and returns; mat_d is not written.  Synchronises the stream and
  * restores the normal limit before returning.  The caller then reads quest_b200_device_status(), which reports
@@ -202,6 +202,24 @@ int quest_b200_prefers_a8(int M, int K, int N);
 int hadamard_quantize_int4_cuda_bf16(void* x_int_packed_ptr, void* scale_ptr, void* x_int_row_sum_ptr,
                                      const void* x_ptr, int group_size, int batch_size, int block,
                                      cudaStream_t stream);
+
+/*
+ * hadamard_quantize_int4_cuda_bf16 with the producer of its input fused in: the rows that are transformed and quantised
+ * are computed on the fly, so the producer's own kernels and one write + one read of [batch_size, group_size] bf16
+ * disappear.  Outputs and their meaning are those of hadamard_quantize_int4_cuda_bf16 applied to y.
+ *   rmsnorm_...   y = bf16( bf16(x * rsqrt(mean_k(x^2) + eps)) * norm_weight )    norm_weight bf16 [group_size]
+ *                 (the model's RMSNorm, src/models/llama.py:64-76, feeding c_attn / w1 / w2)
+ *   silu_mul_...  y = bf16( bf16(silu(gate)) * up ),  silu(v) = v / (1 + exp(-v)) in fp32    gate, up bf16 [batch, group]
+ *                 (the SwiGLU product feeding c_proj, src/models/llama.py:118)
+ * group_size a multiple of block and at most 32768; 16-byte aligned pointers; QB200_ERR_UNSUPPORTED otherwise.
+ * No counterpart in the reference's op package (its layer code quantises a materialised activation tensor).
+ */
+int rmsnorm_hadamard_quantize_int4_cuda_bf16(void* x_int_packed_ptr, void* scale_ptr, void* x_int_row_sum_ptr,
+                                             const void* x_ptr, const void* norm_weight_ptr, float eps, int group_size,
+                                             int batch_size, int block, cudaStream_t stream);
+int silu_mul_hadamard_quantize_int4_cuda_bf16(void* x_int_packed_ptr, void* scale_ptr, void* x_int_row_sum_ptr,
+                                              const void* gate_ptr, const void* up_ptr, int group_size, int batch_size,
+                                              int block, cudaStream_t stream);
 
 /*
  * out = bf16(H_block . x) blockwise along the last dimension (out may alias x).

@@ -228,6 +228,60 @@ def hadamard_quantize_int4(
     return x_int_packed, scale, x_int_row_sum
 
 
+def _quant_outputs(m: int, k: int, like: torch.Tensor, x_int_packed, scale, x_int_row_sum):
+    if x_int_packed is None:
+        x_int_packed = torch.empty(m, k // 2, dtype=torch.uint8, device=like.device)
+    if scale is None:
+        scale = torch.empty(m, 1, dtype=like.dtype, device=like.device)
+    if x_int_row_sum is None:
+        x_int_row_sum = torch.empty(m, 1, dtype=torch.int32, device=like.device)
+    assert scale.dtype == torch.bfloat16 and x_int_packed.dtype == torch.uint8 and x_int_row_sum.dtype == torch.int32
+    assert scale.is_contiguous() and x_int_packed.is_contiguous() and x_int_row_sum.is_contiguous()
+    return x_int_packed, scale, x_int_row_sum
+
+
+def rmsnorm_hadamard_quantize_int4(
+        x: torch.Tensor,
+        norm_weight: torch.Tensor,
+        eps: float,
+        block: int = 128,
+        x_int_packed: torch.Tensor = None,
+        scale: torch.Tensor = None,
+        x_int_row_sum: torch.Tensor = None,
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """``hadamard_quantize_int4(RMSNorm(x))`` in one kernel: y = ((x.float() * rsqrt(mean(x^2) + eps)).type_as(x)
+    * norm_weight) is never written to memory (the RMSNorm of src/models/llama.py:64-76).  x [M, K] bf16,
+    norm_weight [K] bf16.  Returns (x_int_packed, scale, x_int_row_sum) of y."""
+    assert x.dim() == 2 and x.dtype == torch.bfloat16 and x.is_contiguous()
+    assert norm_weight.dtype == torch.bfloat16 and norm_weight.is_contiguous() and norm_weight.numel() == x.size(1)
+    m, k = x.shape
+    x_int_packed, scale, x_int_row_sum = _quant_outputs(m, k, x, x_int_packed, scale, x_int_row_sum)
+    dev = _lib.require_cuda(x, norm_weight, scale, x_int_packed, x_int_row_sum)
+    _call("rmsnorm_hadamard_quantize_int4_cuda_bf16", dev, _lib.ptr(x_int_packed), _lib.ptr(scale), _lib.ptr(x_int_row_sum),
+          _lib.ptr(x), _lib.ptr(norm_weight), float(eps), k, m, int(block), _lib.stream_of(x))
+    return x_int_packed, scale, x_int_row_sum
+
+
+def silu_mul_hadamard_quantize_int4(
+        gate: torch.Tensor,
+        up: torch.Tensor,
+        block: int = 128,
+        x_int_packed: torch.Tensor = None,
+        scale: torch.Tensor = None,
+        x_int_row_sum: torch.Tensor = None,
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """``hadamard_quantize_int4(silu(gate) * up)`` in one kernel (the SwiGLU product of src/models/llama.py:118 is never
+    written to memory).  gate, up [M, K] bf16.  Returns (x_int_packed, scale, x_int_row_sum) of the product."""
+    assert gate.dim() == 2 and gate.shape == up.shape and gate.dtype == torch.bfloat16 and up.dtype == torch.bfloat16
+    assert gate.is_contiguous() and up.is_contiguous()
+    m, k = gate.shape
+    x_int_packed, scale, x_int_row_sum = _quant_outputs(m, k, gate, x_int_packed, scale, x_int_row_sum)
+    dev = _lib.require_cuda(gate, up, scale, x_int_packed, x_int_row_sum)
+    _call("silu_mul_hadamard_quantize_int4_cuda_bf16", dev, _lib.ptr(x_int_packed), _lib.ptr(scale), _lib.ptr(x_int_row_sum),
+          _lib.ptr(gate), _lib.ptr(up), k, m, int(block), _lib.stream_of(gate))
+    return x_int_packed, scale, x_int_row_sum
+
+
 def prefers_a8(m: int, k: int, n: int) -> bool:
     """Whether the int8-operand route (``hadamard_quantize_a8`` + ``fused_matmul_dequantize_a8``) is the faster one
     for a layer of this shape."""

@@ -26,6 +26,8 @@
 //
 // Replaces gemm-quest/quest/matmul_kernel.cu:8-63 and gemm-quest/quest/fused_matmul_dequantize_kernel.cu
 // with gemm-quest/include/symmetric/** (CUTLASS 2.x Sm80 mma.sync kernels).
+#include <string.h>
+
 #include "tcgen05.cuh"
 
 namespace qb {
@@ -70,7 +72,8 @@ struct Cfg {
     static constexpr int U_BYTES = ROWS * U8_ROW;
     static constexpr int TMEM_COLS = (2 * BN > 256) ? 512 : 256;  // two accumulator buffers, power of two
     static constexpr int NUM_BARS = 2 * P_STAGES + 2 * U_STAGES + 4 + 1 + 4;
-    static constexpr int VEC_BYTES = 2 * BN * 8;         // per accumulator buffer: b_add (int32) and b_mul (fp32) of the tile
+    static constexpr int VEC_STRIDE = BN * 8;            // per accumulator buffer: b_add (int32) and b_mul (fp32) of the tile
+    static constexpr int VEC_BYTES = 2 * VEC_STRIDE;
     static constexpr int SMEM_BYTES = 1024 /*alignment slack*/ + U_STAGES * U_BYTES + P_STAGES * P_BYTES + VEC_BYTES + NUM_BARS * 8 + 16;
     // instruction descriptor: D=s32, A=B=s8, both K-major, N and M of the MMA
     static constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
@@ -91,6 +94,7 @@ struct EpilogueParams {
     int32_t* scratch;       // [tile * splits + range][slab_rows][256 columns] int32 partial sums
     int slab_ints;          // slab_rows * 256: a slab holds only the rows a tile can have (M rounded up to 8, at most 128)
     int* counters;          // one per output tile, all zero between launches
+    int tma_store;          // 256 x 256 kernel, fused: the output tensor map is valid (the last tile leaves as bulk tensor stores)
     int test_skip_producer; // tests only: the TMA producer issues nothing, so that every bounded wait of the launch runs out
 };
 
@@ -105,6 +109,29 @@ __device__ __forceinline__ void stg256(void* p, const uint32_t* w) {
                  "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
 }
 
+// The dequantising expression for 32 consecutive accumulators of one output row, as 16 bf16 pairs:
+//   D = bf16( float(2*acc + a_add[m] + b_add[n]) * (0.5f * a_mul[m] * b_mul[n]) )
+// (A variant that replaced the int-to-float conversion by a magic-number addition in packed f32x2 arithmetic measured 1-4 %
+// slower per launch: the conversion is not what limits the epilogue.)
+__device__ __forceinline__ void dequant_chunk(const uint32_t (&r)[32], int a_add, float half_a_mul, const int* sb_add,
+                                              const float* sb_mul, uint32_t (&w)[16]) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        const int4 b0 = *reinterpret_cast<const int4*>(sb_add + 8 * g);
+        const int4 b1 = *reinterpret_cast<const int4*>(sb_add + 8 * g + 4);
+        const float4 m0 = *reinterpret_cast<const float4*>(sb_mul + 8 * g);
+        const float4 m1 = *reinterpret_cast<const float4*>(sb_mul + 8 * g + 4);
+        const int ba[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        const float bm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)  // acc >> 7 == 2 * (acc >> 8): the accumulator is a multiple of 256
+            v[i] = (float)(((int)r[8 * g + i] >> 7) + a_add + ba[i]) * (half_a_mul * bm[i]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) w[4 * g + i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+    }
+}
+
 template <bool FUSED>
 __device__ __forceinline__ void epilogue_store_chunk(const uint32_t (&r)[32], const EpilogueParams& ep, int row, int col0,
                                                      int N, int a_add, float half_a_mul, const int* sb_add,
@@ -112,21 +139,7 @@ __device__ __forceinline__ void epilogue_store_chunk(const uint32_t (&r)[32], co
     if (FUSED) {
         __nv_bfloat16* out = static_cast<__nv_bfloat16*>(ep.out) + (size_t)row * ep.ld + col0;
         uint32_t w[16];  // the 32 results as bf16 pairs
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-            const int4 b0 = *reinterpret_cast<const int4*>(sb_add + 8 * g);
-            const int4 b1 = *reinterpret_cast<const int4*>(sb_add + 8 * g + 4);
-            const float4 m0 = *reinterpret_cast<const float4*>(sb_mul + 8 * g);
-            const float4 m1 = *reinterpret_cast<const float4*>(sb_mul + 8 * g + 4);
-            const int ba[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-            const float bm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
-            float v[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i)  // acc >> 7 == 2 * (acc >> 8): the accumulator is a multiple of 256
-                v[i] = (float)(((int)r[8 * g + i] >> 7) + a_add + ba[i]) * (half_a_mul * bm[i]);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) w[4 * g + i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
-        }
+        dequant_chunk(r, a_add, half_a_mul, sb_add, sb_mul, w);
         if (ep.vec_ok == 2 && col0 + 32 <= N) {
             stg256(out, w);
             stg256(out + 16, w + 8);
@@ -332,8 +345,8 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const bool row_ok = row < M;
             int a_add = 0;
             float half_a_mul = 0.f;
-            int* sb_add = reinterpret_cast<int*>(vec_ptr + acc * (BN * 8));
-            float* sb_mul = reinterpret_cast<float*>(vec_ptr + acc * (BN * 8) + BN * 4);
+            int* sb_add = reinterpret_cast<int*>(vec_ptr + acc * C::VEC_STRIDE);
+            float* sb_mul = reinterpret_cast<float*>(vec_ptr + acc * C::VEC_STRIDE + BN * 4);
             if (FUSED) {
                 // Everything the epilogue needs besides the accumulators is fetched while the tile is still being
                 // accumulated: this tile's per-column vectors go to shared memory, the per-row pair to registers.
@@ -585,7 +598,7 @@ constexpr int kWarps = kFirstPush + kPushWarps;
 constexpr int kThreads = kWarps * 32;
 constexpr int VEC_BYTES = TN * 8;
 constexpr int A_STAGES = 3;  // A8 variant: ring of the int8 A tiles (two in the A halves of the int8 stages, one behind the packed B ring)
-constexpr int NUM_BARS = 2 * P_STAGES + 2 * U_STAGES + 2 + 1 + 4 + 2 * A_STAGES + 1;
+constexpr int NUM_BARS = 2 * P_STAGES + 2 * U_STAGES + 2 + 1 + 4 + 2 * A_STAGES;
 constexpr int LAYOUT_BYTES = U_STAGES * U_BYTES + P_STAGES * P_BYTES + VEC_BYTES + NUM_BARS * 8 + 16;
 constexpr int SMEM_BYTES = 232448;  // all the shared memory one CTA can have; the layout needs a 1024-byte aligned start
 static_assert(LAYOUT_BYTES <= SMEM_BYTES, "layout does not fit");
@@ -617,6 +630,63 @@ __device__ __noinline__ void push_tile_rows(const EpilogueParams& ep, int m0, in
     }
 }
 
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until the bulk stores issued by this thread have read their shared-memory source (their global writes complete
+// on their own, at the latest when the grid ends): enough to let the CTA go.
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+
+// One warp's share of a 256 x 256 tile: its 32 rows (tensor-memory lanes) x the columns [c_begin, c_end), in pieces of 64.
+// stage_base == 0: every thread stores its row's results itself (32-byte pieces).  stage_base != 0 (fused output, the
+// CTA's last tile, when the shared-memory rings are no longer needed): the warp writes each 32 x 64 piece as bf16 into
+// its own 4 KB slab of shared memory in the 128-byte-swizzled layout and one bulk tensor store moves the slab to the
+// output as whole 128-byte lines; rows and columns outside the matrix are clipped by the tensor map.  Per-thread
+// 32-byte stores to 32 different rows per instruction cost the store path about 3 us per tile; the bulk stores do not.
+template <bool FUSED>
+__device__ __forceinline__ void wide_convert_columns(const EpilogueParams& ep, const CUtensorMap* tmap_d, uint32_t t_row,
+                                                     int row, bool row_ok, int a_add, float half_a_mul, const int* sb_add,
+                                                     const float* sb_mul, int n0, int N, int c_begin, int c_end,
+                                                     uint32_t stage_base, int warp_row0, int lane) {
+#pragma unroll 1
+    for (int c0 = c_begin; c0 < c_end; c0 += 64) {
+        if (n0 + c0 >= N) break;  // warp-uniform
+        uint32_t r0[32], r1[32];
+        tmem_ld32(t_row + c0, r0);
+        tmem_ld32(t_row + c0 + 32, r1);
+        tmem_ld_wait();
+        if (FUSED && stage_base != 0) {
+            const uint32_t slab = stage_base + (uint32_t)(c0 >> 6) * 4096u;
+            if (row_ok) {
+                const uint32_t rowaddr = slab + lane * 128;
+                uint32_t w[16];
+                dequant_chunk(r0, a_add, half_a_mul, sb_add + c0, sb_mul + c0, w);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    sts128(rowaddr + ((j ^ (lane & 7)) << 4), make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]));
+                dequant_chunk(r1, a_add, half_a_mul, sb_add + c0 + 32, sb_mul + c0 + 32, w);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    sts128(rowaddr + (((4 + j) ^ (lane & 7)) << 4), make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]));
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_2d(tmap_d, slab, n0 + c0, warp_row0);
+                bulk_commit_group();
+            }
+            continue;
+        }
+        if (!row_ok) continue;
+        epilogue_store_chunk<FUSED>(r0, ep, row, n0 + c0, N, a_add, half_a_mul, sb_add + c0, sb_mul + c0);
+        if (n0 + c0 + 32 < N)
+            epilogue_store_chunk<FUSED>(r1, ep, row, n0 + c0 + 32, N, a_add, half_a_mul, sb_add + c0 + 32, sb_mul + c0 + 32);
+    }
+    if (FUSED && stage_base != 0 && lane == 0) bulk_wait_read_all();  // the slabs have been read before the CTA ends
+}
+
 // PUSH: the multi-GPU variant (two more warps that copy finished tiles to the peers, helped by the epilogue warps on
 // a CTA's last tile); the single-GPU instantiation carries none of that code and is launched without those warps.
 // A8 (single GPU only): the A operand arrives already as int8 in operand order (see hadamard_quant_tc_kernel<HB, true>):
@@ -625,7 +695,8 @@ __device__ __noinline__ void push_tile_rows(const EpilogueParams& ep, int m0, in
 template <bool FUSED, bool PUSH, bool A8 = false>
 __global__ void __launch_bounds__(PUSH ? wide::kThreads : (A8 ? wide::kThreads - 32 : wide::kThreads - 32 * wide::kPushWarps), 1)
 gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                    const __grid_constant__ EpilogueParams ep, const int M, const int N, const int K) {
+                    const __grid_constant__ CUtensorMap tmap_d, const __grid_constant__ EpilogueParams ep, const int M,
+                    const int N, const int K) {
     using namespace wide;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_base = smem_u32(smem_raw);
@@ -649,8 +720,7 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const uint32_t push_free = out_ready + 16;  // [2]
     const uint32_t full_a = push_free + 16;      // [A_STAGES] A8 only
     const uint32_t empty_a = full_a + 8 * A_STAGES;
-    const uint32_t vec_ready = empty_a + 8 * A_STAGES;  // epilogue warps -> unpack warps: this tile's column vectors are staged
-    const uint32_t tmem_slot = vec_ready + 8;
+    const uint32_t tmem_slot = empty_a + 8 * A_STAGES;
     volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - raw_base));
     volatile int* epi_abort = reinterpret_cast<volatile int*>(smem_raw + (tmem_slot + 12 - raw_base));  // see gemm_i4_kernel
     // A8: packed B stages are compact (TN * 64 bytes each), which leaves room for a third A slot behind them
@@ -663,11 +733,6 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const int tiles_n = (N + TN - 1) / TN;
     const int num_tiles = tiles_m * tiles_n;
     const int num_kb = (K + BK - 1) / BK;
-    // The CTA's last tile: with nothing left to unpack, the unpack warps convert and store half of its columns.  Needs at
-    // least four K stages, so that a wait on the tile's barriers by parity cannot be answered by an older phase.
-    const int last_tile = (int)blockIdx.x < num_tiles
-                              ? (int)blockIdx.x + ((num_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x) * (int)gridDim.x : -1;
-    const bool help_last = !PUSH && num_kb >= 4;
     uint32_t pre_issued = 0;  // producer thread: copies already issued before the CTA-wide synchronisation
 
     if (threadIdx.x == 0) {
@@ -687,7 +752,6 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         mbar_init(tmem_full, 1);
         mbar_init(tmem_empty, kEpiWarps);
         mbar_init(mma_done, 1);
-        mbar_init(vec_ready, kEpiWarps);
         for (int i = 0; i < 2; ++i) {
             mbar_init(out_ready + 8 * i, kEpiWarps);
             mbar_init(push_free + 8 * i, kPushWarps);
@@ -811,31 +875,18 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     half_a_mul = 0.5f * bf16_to_f32(ep.a_mul[row]);
                 }
             }
-            if (FUSED) {  // tell the unpack warps (which help with the CTA's last tile) that this warp's share is staged
-                __syncwarp();
-                if (lane == 0) mbar_arrive(vec_ready);
-            }
             ok = mbar_wait(tmem_full, local_tile & 1u, 6);
             if (!ok) *epi_abort = 1;
             asm volatile("bar.sync 2, %0;" ::"n"(kEpiWarps * 32) : "memory");  // vectors staged; uniform give-up decision
             if (*epi_abort) break;
             tc_fence_after();
             const uint32_t t_row = tmem_acc + ((uint32_t)(quad * 32) << 16) + half * TN;
-            const int c_end = (help_last && tile == last_tile) ? TN / 2 : TN;  // the unpack warps take the other half
-            if (m0 + half * 128 < M) {  // warp-uniform: otherwise this accumulator was not computed
-#pragma unroll 1
-                for (int c0 = 0; c0 < c_end; c0 += 64) {
-                    if (n0 + c0 >= N) break;
-                    uint32_t r0[32], r1[32];
-                    tmem_ld32(t_row + c0, r0);
-                    tmem_ld32(t_row + c0 + 32, r1);
-                    tmem_ld_wait();
-                    if (!row_ok) continue;
-                    epilogue_store_chunk<FUSED>(r0, ep, row, n0 + c0, N, a_add, half_a_mul, sb_add + c0, sb_mul + c0);
-                    if (n0 + c0 + 32 < N)
-                        epilogue_store_chunk<FUSED>(r1, ep, row, n0 + c0 + 32, N, a_add, half_a_mul, sb_add + c0 + 32, sb_mul + c0 + 32);
-                }
-            }
+            // The CTA's last tile leaves through shared memory: the int8 ring is free once the tile's MMAs have completed.
+            const bool last = !PUSH && tile + (int)gridDim.x >= num_tiles;
+            const uint32_t stage_base = (FUSED && last && ep.tma_store) ? u_base + (uint32_t)(half * 4 + quad) * 16384u : 0u;
+            if (m0 + half * 128 < M)  // warp-uniform: otherwise this accumulator was not computed
+                wide_convert_columns<FUSED>(ep, &tmap_d, t_row, row, row_ok, a_add, half_a_mul, sb_add, sb_mul, n0, N, 0, TN,
+                                            stage_base, m0 + half * 128 + quad * 32, lane);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tmem_empty);
@@ -936,46 +987,6 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 if (lane == 0) {
                     mbar_arrive(full_u + 8 * us);
                     mbar_arrive(empty_p + 8 * ps);
-                }
-            }
-        }
-        // Nothing is left to unpack: convert and store columns TN/2 .. TN-1 of the CTA's last tile while the epilogue warps
-        // handle the first half.  Warp u of the unpack group stands beside epilogue warp u: same accumulator (u >> 2), and
-        // the tensor-memory lane quadrant its own warp index allows.
-        if (help_last && ok && last_tile >= 0) {
-            const uint32_t lt = (uint32_t)((last_tile - (int)blockIdx.x) / (int)gridDim.x);  // how many tiles came before it
-            const int m0 = (last_tile % tiles_m) * TM;
-            const int n0 = (last_tile / tiles_m) * TN;
-            const int quad = warp & 3;
-            const int half = (warp - kFirstUnpack) >> 2;
-            const int row = m0 + half * 128 + quad * 32 + lane;
-            const bool row_ok = row < M;
-            int a_add = 0;
-            float half_a_mul = 0.f;
-            if (FUSED && row_ok) {
-                a_add = ep.a_add[row];
-                half_a_mul = 0.5f * bf16_to_f32(ep.a_mul[row]);
-            }
-            const uint8_t* vec_ptr = smem_raw + (vec_base - raw_base);
-            const int* sb_add = reinterpret_cast<const int*>(vec_ptr);
-            const float* sb_mul = reinterpret_cast<const float*>(vec_ptr + TN * 4);
-            if (FUSED) ok = mbar_wait(vec_ready, lt & 1u, 22);
-            ok = ok && mbar_wait(tmem_full, lt & 1u, 23);
-            ok = __all_sync(0xffffffffu, ok);
-            if (ok && m0 + half * 128 < M) {
-                tc_fence_after();
-                const uint32_t t_row = tmem_acc + ((uint32_t)(quad * 32) << 16) + half * TN;
-#pragma unroll 1
-                for (int c0 = TN / 2; c0 < TN; c0 += 64) {
-                    if (n0 + c0 >= N) break;
-                    uint32_t r0[32], r1[32];
-                    tmem_ld32(t_row + c0, r0);
-                    tmem_ld32(t_row + c0 + 32, r1);
-                    tmem_ld_wait();
-                    if (!row_ok) continue;
-                    epilogue_store_chunk<FUSED>(r0, ep, row, n0 + c0, N, a_add, half_a_mul, sb_add + c0, sb_mul + c0);
-                    if (n0 + c0 + 32 < N)
-                        epilogue_store_chunk<FUSED>(r1, ep, row, n0 + c0 + 32, N, a_add, half_a_mul, sb_add + c0 + 32, sb_mul + c0 + 32);
                 }
             }
         }
@@ -1152,6 +1163,28 @@ static int pick_splits(int M, int N, int K, int sms) {
     return s >= 2 ? (int)s : 1;
 }
 
+// Fused output D as bf16 [M, N] with row pitch ld: box = 64 columns (128 bytes, the swizzle span) x 32 rows, the piece one
+// warp of the 256 x 256 kernel stores at a time.  Returns false (and leaves ep->tma_store 0) where a tensor map cannot
+// describe the output: the kernel then keeps to per-thread stores.  QB200_GEMM_TMA_STORE=0 switches the bulk stores off.
+static bool make_output_map(CUtensorMap* map, EpilogueParams* ep, int M, int N) {
+    memset(map, 0, sizeof(*map));
+    ep->tma_store = 0;
+    if (ep->n_peer > 0 || !aligned16(ep->out) || ep->ld % 8 != 0) return false;
+    if (const char* e = getenv("QB200_GEMM_TMA_STORE"))
+        if (e[0] == '0') return false;
+    EncodeTiledFn fn = get_encode_fn();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+    const cuuint64_t strides[1] = {(cuuint64_t)ep->ld * 2};
+    const cuuint32_t box[2] = {64, 32};
+    const cuuint32_t estr[2] = {1, 1};
+    if (fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ep->out, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    ep->tma_store = 1;
+    return true;
+}
+
 // A operand as int8 [rows, K] row-major; box = 128 bytes (one K stage, the swizzle span) x 256 rows.
 static int make_a8_map(CUtensorMap* map, const void* base, int rows, int K) {
     EncodeTiledFn fn = get_encode_fn();
@@ -1166,8 +1199,9 @@ static int make_a8_map(CUtensorMap* map, const void* base, int rows, int K) {
     return r == CUDA_SUCCESS ? QB200_OK : QB200_ERR_DRIVER;
 }
 
-static int launch_gemm_wide_a8(const EpilogueParams& ep, const void* a8, const void* b, int M, int K, int N, int sms,
+static int launch_gemm_wide_a8(const EpilogueParams& ep_in, const void* a8, const void* b, int M, int K, int N, int sms,
                                int dev, cudaStream_t stream) {
+    EpilogueParams ep = ep_in;
     static bool attr_set[64] = {false};
     auto kernel = gemm_i4_wide_kernel<true, false, true>;
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
@@ -1180,15 +1214,18 @@ static int launch_gemm_wide_a8(const EpilogueParams& ep, const void* a8, const v
     if (st != QB200_OK) return st;
     st = make_packed_map(&mb, b, N, K, wide::TN);
     if (st != QB200_OK) return st;
+    CUtensorMap md;
+    make_output_map(&md, &ep, M, N);
     const int tiles = ((M + wide::TM - 1) / wide::TM) * ((N + wide::TN - 1) / wide::TN);
     const int grid = tiles < sms ? tiles : sms;
-    kernel<<<grid, wide::kThreads - 32, wide::SMEM_BYTES, stream>>>(ma, mb, ep, M, N, K);
+    kernel<<<grid, wide::kThreads - 32, wide::SMEM_BYTES, stream>>>(ma, mb, md, ep, M, N, K);
     return launch_status();
 }
 
 template <bool FUSED, bool PUSH>
-static int launch_gemm_wide_impl(const EpilogueParams& ep, const void* a, const void* b, int M, int K, int N, int sms,
+static int launch_gemm_wide_impl(const EpilogueParams& ep_in, const void* a, const void* b, int M, int K, int N, int sms,
                                  int dev, cudaStream_t stream) {
+    EpilogueParams ep = ep_in;
     static bool attr_set[64] = {false};
     auto kernel = gemm_i4_wide_kernel<FUSED, PUSH>;
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
@@ -1204,7 +1241,10 @@ static int launch_gemm_wide_impl(const EpilogueParams& ep, const void* a, const 
     const int tiles = ((M + wide::TM - 1) / wide::TM) * ((N + wide::TN - 1) / wide::TN);
     const int grid = tiles < sms ? tiles : sms;
     const int threads = PUSH ? wide::kThreads : wide::kThreads - 32 * wide::kPushWarps;
-    kernel<<<grid, threads, wide::SMEM_BYTES, stream>>>(ma, mb, ep, M, N, K);
+    CUtensorMap md;
+    if (FUSED && !PUSH) make_output_map(&md, &ep, M, N);
+    else memset(&md, 0, sizeof(md));
+    kernel<<<grid, threads, wide::SMEM_BYTES, stream>>>(ma, mb, md, ep, M, N, K);
     return launch_status();
 }
 
@@ -1472,7 +1512,7 @@ extern "C" int quest_b200_test_bounded_wait_cuda(void* mat_d, const void* mat_a,
                                                  const void* vec_b_add, const void* vec_a_mul, const void* vec_b_mul, int M,
                                                  int K, int N, long long wait_limit_cycles, cudaStream_t stream) {
     if (M <= 0 || N <= 0 || K <= 0 || !vec_a_add || !vec_b_add || !vec_a_mul || !vec_b_mul) return QB200_ERR_INVALID_ARGUMENT;
-    if (wait_limit_cycles <= 0 || wait_limit_cycles > kWaitLimitCycles) return QB200_ERR_INVALID_ARGUMENT;
+    if (wait_limit_cycles < kWaitLimitFloor || wait_limit_cycles > kWaitLimitCycles) return QB200_ERR_INVALID_ARGUMENT;
     if (cudaDeviceSynchronize() != cudaSuccess) return QB200_ERR_CUDA;
     int st = set_wait_limit_cycles(wait_limit_cycles);
     if (st != QB200_OK) return st;

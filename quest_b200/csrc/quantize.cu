@@ -27,6 +27,9 @@ struct RowParams {
     int32_t* row_sum;              // optional [M]
     int K;
     int M;
+    const __nv_bfloat16* x2;       // producer-fused kernels: second input [M,K] (the "up" branch of SiLU(gate) * up)
+    const __nv_bfloat16* norm_w;   // producer-fused kernels: RMSNorm weight [K]
+    float norm_eps;                // RMSNorm epsilon
     float had_scale;               // Hadamard normalisation constant
     int x_out_mode;                // 0 none, 1 transformed values, 2 dequantised values
     int quantize;                  // 0: stop after the scale (find_scale / transform only)
@@ -338,12 +341,23 @@ __device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) { f32x2 r; asm("mul.rn.f
 __device__ __forceinline__ f32x2 add2_rd(f32x2 a, f32x2 b) { f32x2 r; asm("add.rm.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
 __device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) { f32x2 r; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c)); return r; }
 
-template <int HB, int UNITS>
+// PRO: what produces the rows that are transformed and quantised.
+//   0  the input itself.
+//   1  RMSNorm of the input:  y = bf16( bf16(x * rsqrt(mean(x^2) + eps)) * w )   (src/models/llama.py:64-76: the
+//      normalised value is cast back to the activation type before the weight multiplies it).
+//   2  SwiGLU gate:           y = bf16( bf16(silu(x)) * x2 ),  silu(x) = x / (1 + exp(-x)) in fp32
+//      (src/models/llama.py:118, torch's silu for bf16 inputs).
+// The producer rewrites the row in shared memory, in place, between the copy and the tensor-core stage; everything
+// after it is unchanged.  It saves the producer's own kernel(s), one write and one read of [M, K] bf16.
+constexpr int kProNone = 0, kProRmsNorm = 1, kProSiluMul = 2;
+
+template <int HB, int UNITS, int PRO = kProNone>
 __global__ void __launch_bounds__(256, UNITS == 1 ? 4 : (UNITS == 2 ? 3 : 2))
 hadamard_quant_mma_kernel(const RowParams p, const int W, const int G, const int nbuf) {
     extern __shared__ __align__(16) uint8_t hq_smem[];
     __shared__ float part_ssq[2][8];  // indexed by batch parity: one barrier per batch is enough
     __shared__ int part_rs[2][8];
+    __shared__ float part_norm[8];    // PRO == kProRmsNorm: the warps' partial sums of squares of the raw row
 
 #ifdef QB200_TRACE
     if (threadIdx.x == 0) {
@@ -418,6 +432,73 @@ hadamard_quant_mma_kernel(const RowParams p, const int W, const int G, const int
             asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncwarp();
+
+        if (PRO != kProNone) {
+            // Each lane owns the 16-byte chunks it copied itself (chunk c = 32 j + lane of every unit).
+            float rinv = 0.f;
+            if (PRO == kProRmsNorm) {
+                float nsq = 0.f;
+#pragma unroll
+                for (int u = 0; u < UNITS; ++u) {
+                    const uint32_t in_base = smem_w + u * step_bytes + buf * kStepIn;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int c = j * 32 + lane;
+                        const uint4 q = lds128(in_base + (c >> 4) * kBlkPitch + (c & 15) * 16);  // zero beyond K
+                        const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float a = bf16lo_to_f32(w4[i]), b = bf16hi_to_f32(w4[i]);
+                            nsq = fmaf(a, a, nsq);
+                            nsq = fmaf(b, b, nsq);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int m2 = 16; m2 > 0; m2 >>= 1) nsq += __shfl_xor_sync(0xffffffffu, nsq, m2);
+                if (W > 1) {  // block-uniform: the row is spread over W warps
+                    if (lane == 0) part_norm[warp] = nsq;
+                    __syncthreads();
+                    nsq = 0.f;
+                    for (int i = 0; i < W; ++i) nsq += part_norm[grp * W + i];
+                    __syncthreads();  // part_norm is rewritten for the next batch
+                }
+                rinv = rsqrtf(__fdiv_rn(nsq, (float)K) + p.norm_eps);
+            }
+            const int row_p = batch * G + grp;
+#pragma unroll
+            for (int u = 0; u < UNITS; ++u) {
+                const int unit = u * W + wig;
+                const uint32_t in_base = smem_w + u * step_bytes + buf * kStepIn;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int c = j * 32 + lane;
+                    const int e = unit * kUnit + c * 8;
+                    if (e >= K || row_p >= M) continue;
+                    const uint32_t addr = in_base + (c >> 4) * kBlkPitch + (c & 15) * 16;
+                    const uint4 q = lds128(addr);
+                    const uint4 o = PRO == kProRmsNorm ? __ldg(reinterpret_cast<const uint4*>(p.norm_w + e))
+                                                       : ld_stream16(p.x2 + (size_t)row_p * K + e);
+                    const uint32_t w4[4] = {q.x, q.y, q.z, q.w}, o4[4] = {o.x, o.y, o.z, o.w};
+                    uint32_t y4[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        float a = bf16lo_to_f32(w4[i]), b = bf16hi_to_f32(w4[i]);
+                        if (PRO == kProRmsNorm) {
+                            a *= rinv;
+                            b *= rinv;
+                        } else {
+                            a = __fdiv_rn(a, 1.f + expf(-a));
+                            b = __fdiv_rn(b, 1.f + expf(-b));
+                        }
+                        const uint32_t t = pack_bf16x2(a, b);  // the producer's first rounding to the activation type
+                        y4[i] = pack_bf16x2(bf16lo_to_f32(t) * bf16lo_to_f32(o4[i]), bf16hi_to_f32(t) * bf16hi_to_f32(o4[i]));
+                    }
+                    sts128(addr, make_uint4(y4[0], y4[1], y4[2], y4[3]));
+                }
+            }
+            __syncwarp();  // ldmatrix below reads chunks written by other lanes of this warp
+        }
 
         uint32_t v[UNITS][16];  // v[u][2a + nu]: elements 16a + 4tig + 2nu (+1) of block g of the unit
         f32x2 ssq2 = 0ull;
@@ -599,7 +680,7 @@ hadamard_quant_mma_kernel(const RowParams p, const int W, const int G, const int
 template <int HB, bool EXTRAS>
 static int launch_row(const RowParams& p, cudaStream_t stream);
 
-template <int HB>
+template <int HB, int PRO = kProNone>
 static int launch_hq_mma(const RowParams& p, cudaStream_t stream) {
     const int units = (p.K + kUnit - 1) / kUnit;
     // units per warp, warps per row, rows per block (at most 16 warps per block)
@@ -608,7 +689,7 @@ static int launch_hq_mma(const RowParams& p, cudaStream_t stream) {
     if (per != 1 && per != 2 && per != 4) per = 2;
     int W = (units + per - 1) / per;
     if (W > 8 && per < 4) { per = 4; W = (units + per - 1) / per; }
-    if (W > 8) return launch_row<HB, false>(p, stream);  // very long rows: shuffle-butterfly kernel
+    if (W > 8) return PRO != kProNone ? QB200_ERR_UNSUPPORTED : launch_row<HB, false>(p, stream);  // very long rows: shuffle-butterfly kernel
     // Rows per block: up to 8 warps per block, but few rows overall want small blocks so that every SM ends
     // at the same time (a block is the unit the rows are dealt out in).
     int G = 8 / W;
@@ -617,7 +698,7 @@ static int launch_hq_mma(const RowParams& p, cudaStream_t stream) {
     if (G > p.M) G = p.M;
     const int warps = W * G;
     const long long batches = ((long long)p.M + G - 1) / G;
-    if ((size_t)warps * per * kStepBytes > kMaxDynSmem) return launch_row<HB, false>(p, stream);
+    if ((size_t)warps * per * kStepBytes > kMaxDynSmem) return PRO != kProNone ? QB200_ERR_UNSUPPORTED : launch_row<HB, false>(p, stream);
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) != cudaSuccess) return QB200_ERR_CUDA;
     {
@@ -662,9 +743,9 @@ static int launch_hq_mma(const RowParams& p, cudaStream_t stream) {
         kernel<<<(unsigned)grid, 32 * warps, (size_t)warps * per * nbuf * kStepIn, stream>>>(p, W, G, nbuf);
         return launch_status();
     };
-    if (per == 1) return launch(hadamard_quant_mma_kernel<HB, 1>, 0);
-    if (per == 2) return launch(hadamard_quant_mma_kernel<HB, 2>, 1);
-    return launch(hadamard_quant_mma_kernel<HB, 4>, 2);
+    if (per == 1) return launch(hadamard_quant_mma_kernel<HB, 1, PRO>, 0);
+    if (per == 2) return launch(hadamard_quant_mma_kernel<HB, 2, PRO>, 1);
+    return launch(hadamard_quant_mma_kernel<HB, 4, PRO>, 2);
 }
 
 // Any K, any alignment, no Hadamard: one block per row, scalar accesses.  Only used for shapes the
@@ -928,6 +1009,67 @@ extern "C" int hadamard_quantize_int4_cuda_bf16(void* x_int_packed_ptr, void* sc
         case 128: return launch_hq_mma<128>(p, stream);
         default: return launch_hq_mma<256>(p, stream);
     }
+}
+
+// Producer-fused variants: the rows that are transformed and quantised are RMSNorm(x) * w, or SiLU(gate) * up, computed
+// on the fly from the kernel's inputs (see hadamard_quant_mma_kernel).
+static int run_producer_hq(RowParams& p, int block, int pro, cudaStream_t stream) {
+    p.quantize = 1;
+    p.had_scale = __bfloat162float(__float2bfloat16_rn((float)(1.0 / sqrt((double)block))));
+    if (!vector_path_ok(p)) return QB200_ERR_UNSUPPORTED;
+    if (pro == kProRmsNorm) {
+        if (!aligned16(p.norm_w)) return QB200_ERR_UNSUPPORTED;
+        switch (block) {
+            case 64: return launch_hq_mma<64, kProRmsNorm>(p, stream);
+            case 128: return launch_hq_mma<128, kProRmsNorm>(p, stream);
+            default: return launch_hq_mma<256, kProRmsNorm>(p, stream);
+        }
+    }
+    if (!aligned16(p.x2)) return QB200_ERR_UNSUPPORTED;
+    switch (block) {
+        case 64: return launch_hq_mma<64, kProSiluMul>(p, stream);
+        case 128: return launch_hq_mma<128, kProSiluMul>(p, stream);
+        default: return launch_hq_mma<256, kProSiluMul>(p, stream);
+    }
+}
+
+extern "C" int rmsnorm_hadamard_quantize_int4_cuda_bf16(void* x_int_packed_ptr, void* scale_ptr, void* x_int_row_sum_ptr,
+                                                        const void* x_ptr, const void* norm_weight_ptr, float eps,
+                                                        int group_size, int batch_size, int block, cudaStream_t stream) {
+    if (group_size < 0 || batch_size < 0) return QB200_ERR_INVALID_ARGUMENT;
+    if (block != 64 && block != 128 && block != 256) return QB200_ERR_UNSUPPORTED;
+    if (batch_size == 0) return QB200_OK;
+    if (!x_int_packed_ptr || !scale_ptr || !x_ptr || !norm_weight_ptr || group_size == 0 || group_size % block != 0)
+        return QB200_ERR_INVALID_ARGUMENT;
+    RowParams p{};
+    p.x = static_cast<const __nv_bfloat16*>(x_ptr);
+    p.norm_w = static_cast<const __nv_bfloat16*>(norm_weight_ptr);
+    p.norm_eps = eps;
+    p.scale_out = static_cast<__nv_bfloat16*>(scale_ptr);
+    p.q_packed = static_cast<uint8_t*>(x_int_packed_ptr);
+    p.row_sum = static_cast<int32_t*>(x_int_row_sum_ptr);
+    p.K = group_size;
+    p.M = batch_size;
+    return run_producer_hq(p, block, kProRmsNorm, stream);
+}
+
+extern "C" int silu_mul_hadamard_quantize_int4_cuda_bf16(void* x_int_packed_ptr, void* scale_ptr, void* x_int_row_sum_ptr,
+                                                         const void* gate_ptr, const void* up_ptr, int group_size,
+                                                         int batch_size, int block, cudaStream_t stream) {
+    if (group_size < 0 || batch_size < 0) return QB200_ERR_INVALID_ARGUMENT;
+    if (block != 64 && block != 128 && block != 256) return QB200_ERR_UNSUPPORTED;
+    if (batch_size == 0) return QB200_OK;
+    if (!x_int_packed_ptr || !scale_ptr || !gate_ptr || !up_ptr || group_size == 0 || group_size % block != 0)
+        return QB200_ERR_INVALID_ARGUMENT;
+    RowParams p{};
+    p.x = static_cast<const __nv_bfloat16*>(gate_ptr);
+    p.x2 = static_cast<const __nv_bfloat16*>(up_ptr);
+    p.scale_out = static_cast<__nv_bfloat16*>(scale_ptr);
+    p.q_packed = static_cast<uint8_t*>(x_int_packed_ptr);
+    p.row_sum = static_cast<int32_t*>(x_int_row_sum_ptr);
+    p.K = group_size;
+    p.M = batch_size;
+    return run_producer_hq(p, block, kProSiluMul, stream);
 }
 
 extern "C" int hadamard_quantize_a8_cuda_bf16(void* a8_ptr, void* scale_ptr, void* x_int_row_sum_ptr, const void* x_ptr,

@@ -52,9 +52,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 
 // Bounded wait: gives up after about a second of polling, records the failure and tells the caller.  The limit is a
-// device variable (one per translation unit) so that a test can shorten it to milliseconds; it is read only on the slow
-// path, after the first poll has failed.
+// device variable (one per translation unit) so that a test can shorten it to milliseconds.  It is read only once a
+// wait has already lasted kWaitLimitFloor cycles (half a millisecond, far beyond any healthy wait): a load of it at
+// the start of every slow-path wait cost the GEMM 2 % of its time.
 constexpr long long kWaitLimitCycles = 2000000000LL;
+constexpr long long kWaitLimitFloor = 1000000LL;  // no limit shorter than this takes effect
 static __device__ long long g_wait_limit_cycles = kWaitLimitCycles;
 
 static inline int set_wait_limit_cycles(long long cycles) {
@@ -64,11 +66,11 @@ static inline int set_wait_limit_cycles(long long cycles) {
 
 static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, int where) {
     const long long t0 = clock64();
-    const long long limit = *reinterpret_cast<volatile long long*>(&g_wait_limit_cycles);
     while (true) {
         for (int i = 0; i < 64; ++i)
             if (mbar_try_wait(bar, parity)) return true;
-        if (clock64() - t0 > limit) {
+        const long long waited = clock64() - t0;
+        if (waited > kWaitLimitFloor && waited > *reinterpret_cast<volatile long long*>(&g_wait_limit_cycles)) {
             atomicCAS(&g_device_status, 0, (where << 8) | QB200_ERR_DEVICE_TIMEOUT);
             return false;
         }
@@ -129,6 +131,18 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// A wait that names the 32 destination registers of a tcgen05.ld, so that no use of them can be scheduled above it
+// (the wait covers every tcgen05.ld issued so far).
+__device__ __forceinline__ void tmem_ld_wait32(uint32_t (&r)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                   "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                   "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+                 :
+                 : "memory");
+}
 
 // 32 lanes x 16 columns; and a wait that names the destination registers, so that no use of them can be scheduled
 // above it (the wait covers every tcgen05.ld issued so far).

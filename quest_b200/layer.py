@@ -165,6 +165,17 @@ class Linear4bit(nn.Module):
         self.register_buffer('w_add', w_add)
         self.register_buffer('w_meta_e', w_meta_e)
 
+    def forward_quantized(self, a_int_packed: torch.Tensor, a_scale: torch.Tensor, a_int_row_sum: torch.Tensor,
+                          out: torch.Tensor = None) -> torch.Tensor:
+        """The layer on activations that are already quantised ([M, K/2] packed codes, [M, 1] scales and row sums, as
+        written by ``hadamard_quantize_int4`` or one of its producer-fused variants): only the fused GEMM runs.  Several
+        layers that read the same activations (w1 and w2 of a SwiGLU block) can share one quantisation this way."""
+        y = quest.fused_matmul_dequantize_int4_int4t_bf16(mat_a=a_int_packed, mat_b=self.w_int_packed, vec_a_add=a_int_row_sum,
+                                                          vec_b_add=self.w_add, vec_a_mul=a_scale, vec_b_mul=self.w_scale, out=out)
+        if self.bias is not None:
+            y += self.bias
+        return y
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if not self.use_noop:
             a = x.contiguous().flatten(end_dim=-2)

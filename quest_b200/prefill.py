@@ -16,7 +16,11 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
-from .layer import Linear4bit
+import quest_b200 as quest
+from .layer import HADAMARD_BLOCK, Linear4bit
+from .workspace import default_cache
+
+FUSED_MODES = ("int4_fused",)  # modes in which the quantiser is fused into the producer of each linear's input
 
 
 @dataclasses.dataclass
@@ -92,8 +96,36 @@ class Block(nn.Module):
         self.ln_2, self.mlp = RMSNorm(cfg.n_embd, cfg.rmsnorm_eps), MLP(cfg)
 
     def forward(self, x, table):
+        if getattr(self, "fused", False):
+            return self.forward_fused(x, table)
         x = x + self.attn(self.ln_1(x), table)
         return x + self.mlp(self.ln_2(x))
+
+    def forward_fused(self, x, table):
+        """The same block with every quantiser fused into the producer of its input: RMSNorm -> quantise is one kernel
+        (its result feeds c_attn, and w1 and w2 share one quantisation), SiLU(w1 x) * w2 x -> quantise is one kernel.
+        Needs W4A4 linears with the Hadamard transform (swap_linears(..., 'int4_fused'))."""
+        B, T, C = x.shape
+
+        def ws(m, k):
+            w = default_cache.get(m, k, x.device, x.dtype)
+            return dict(x_int_packed=w["_a_int_packed"], scale=w["_a_scale"], x_int_row_sum=w["_a_int_row_sum"])
+
+        flat = x.reshape(-1, C)
+        q = quest.rmsnorm_hadamard_quantize_int4(flat, self.ln_1.weight, self.ln_1.eps, HADAMARD_BLOCK, **ws(flat.size(0), C))
+        att = self.attn
+        qkv = att.c_attn.forward_quantized(*q).view(B, T, 3 * C)
+        qh, kh, vh = qkv.split(C, dim=2)
+        qh, kh = apply_rope(qh.view(B, T, att.n_head, -1), kh.view(B, T, att.n_head, -1), table)
+        vh = vh.view(B, T, att.n_head, -1)
+        y = F.scaled_dot_product_attention(qh.transpose(1, 2), kh.transpose(1, 2), vh.transpose(1, 2), is_causal=True)
+        x = x + att.c_proj(y.transpose(1, 2).contiguous().view(B, T, C))
+        flat = x.reshape(-1, C)
+        q = quest.rmsnorm_hadamard_quantize_int4(flat, self.ln_2.weight, self.ln_2.eps, HADAMARD_BLOCK, **ws(flat.size(0), C))
+        gate = self.mlp.w1.forward_quantized(*q)
+        up = self.mlp.w2.forward_quantized(*q)
+        q = quest.silu_mul_hadamard_quantize_int4(gate, up, HADAMARD_BLOCK, **ws(gate.size(0), gate.size(1)))
+        return x + self.mlp.c_proj.forward_quantized(*q).view(B, T, C)
 
 
 class Decoder(nn.Module):
@@ -121,16 +153,21 @@ class Decoder(nn.Module):
 
 def swap_linears(model: Decoder, mode: str = "int4", use_hadamard: bool = True) -> Decoder:
     """Replace every nn.Linear under ``model.transformer`` (gemm-quest/benchmarks/bench_e2e.py:79-96).
-    mode: 'bf16' (leave as is), 'int4' (W4A4 kernels, weights quantised from the current ones), 'noop'."""
+    mode: 'bf16' (leave as is), 'int4' (W4A4 kernels, weights quantised from the current ones), 'int4_fused' (the same
+    linears, with every activation quantiser fused into the kernel that produces the linear's input), 'noop'."""
     if mode == "bf16":
         return model
-    if mode not in ("int4", "noop"):
+    if mode not in ("int4", "noop") + FUSED_MODES:
         raise NotImplementedError(mode)
+    if mode in FUSED_MODES and not use_hadamard:
+        raise ValueError("the producer-fused quantisers include the Hadamard transform")
     targets = [(name, m) for name, m in model.transformer.named_modules() if isinstance(m, nn.Linear)]
     for name, m in targets:
         new = Linear4bit(m.in_features, m.out_features, bias=m.bias is not None, device=m.weight.device,
                          dtype=m.weight.dtype, use_hadamard=use_hadamard, use_noop=(mode == "noop"), weight=m.weight.data)
         model.transformer.set_submodule(name, new)
+    for blk in model.transformer.h:
+        blk.fused = mode in FUSED_MODES
     return model
 
 

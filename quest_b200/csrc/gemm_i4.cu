@@ -638,6 +638,7 @@ __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bul
 // Waits until the bulk stores issued by this thread have read their shared-memory source (their global writes complete
 // on their own, at the latest when the grid ends): enough to let the CTA go.
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // One warp's share of a 256 x 256 tile: its 32 rows (tensor-memory lanes) x the columns [c_begin, c_end), in pieces of 64.
 // stage_base == 0: every thread stores its row's results itself (32-byte pieces).  stage_base != 0 (fused output, the
@@ -645,8 +646,17 @@ __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bu
 // its own 4 KB slab of shared memory in the 128-byte-swizzled layout and one bulk tensor store moves the slab to the
 // output as whole 128-byte lines; rows and columns outside the matrix are clipped by the tensor map.  Per-thread
 // 32-byte stores to 32 different rows per instruction cost the store path about 3 us per tile; the bulk stores do not.
+// Tensor maps of the same output matrix in the memory of the other GPUs (multi-GPU variant only): the staged pieces of a
+// CTA's last tile are stored to them with the same bulk tensor stores as to the local output - plain stores over NVLink,
+// no multicast, issued by the copy engine of the SM instead of by push warps.
+template <bool PUSH>
+struct PeerMaps {
+    CUtensorMap m[PUSH ? 7 : 1];
+};
+
 template <bool FUSED>
-__device__ __forceinline__ void wide_convert_columns(const EpilogueParams& ep, const CUtensorMap* tmap_d, uint32_t t_row,
+__device__ __forceinline__ void wide_convert_columns(const EpilogueParams& ep, const CUtensorMap* tmap_d,
+                                                     const CUtensorMap* peer_maps, int n_peer_maps, uint32_t t_row,
                                                      int row, bool row_ok, int a_add, float half_a_mul, const int* sb_add,
                                                      const float* sb_mul, int n0, int N, int c_begin, int c_end,
                                                      uint32_t stage_base, int warp_row0, int lane) {
@@ -675,6 +685,7 @@ __device__ __forceinline__ void wide_convert_columns(const EpilogueParams& ep, c
             __syncwarp();
             if (lane == 0) {
                 tma_store_2d(tmap_d, slab, n0 + c0, warp_row0);
+                for (int pi = 0; pi < n_peer_maps; ++pi) tma_store_2d(peer_maps + pi, slab, n0 + c0, warp_row0);
                 bulk_commit_group();
             }
             continue;
@@ -684,7 +695,10 @@ __device__ __forceinline__ void wide_convert_columns(const EpilogueParams& ep, c
         if (n0 + c0 + 32 < N)
             epilogue_store_chunk<FUSED>(r1, ep, row, n0 + c0 + 32, N, a_add, half_a_mul, sb_add + c0 + 32, sb_mul + c0 + 32);
     }
-    if (FUSED && stage_base != 0 && lane == 0) bulk_wait_read_all();  // the slabs have been read before the CTA ends
+    if (FUSED && stage_base != 0 && lane == 0) {
+        if (n_peer_maps > 0) bulk_wait_all();  // stores to other GPUs: complete before this thread goes on
+        else bulk_wait_read_all();             // the slabs have been read before the CTA ends
+    }
 }
 
 // PUSH: the multi-GPU variant (two more warps that copy finished tiles to the peers, helped by the epilogue warps on
@@ -695,8 +709,8 @@ __device__ __forceinline__ void wide_convert_columns(const EpilogueParams& ep, c
 template <bool FUSED, bool PUSH, bool A8 = false>
 __global__ void __launch_bounds__(PUSH ? wide::kThreads : (A8 ? wide::kThreads - 32 : wide::kThreads - 32 * wide::kPushWarps), 1)
 gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                    const __grid_constant__ CUtensorMap tmap_d, const __grid_constant__ EpilogueParams ep, const int M,
-                    const int N, const int K) {
+                    const __grid_constant__ CUtensorMap tmap_d, const __grid_constant__ PeerMaps<PUSH> peers,
+                    const __grid_constant__ EpilogueParams ep, const int M, const int N, const int K) {
     using namespace wide;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_base = smem_u32(smem_raw);
@@ -882,16 +896,19 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             tc_fence_after();
             const uint32_t t_row = tmem_acc + ((uint32_t)(quad * 32) << 16) + half * TN;
             // The CTA's last tile leaves through shared memory: the int8 ring is free once the tile's MMAs have completed.
-            const bool last = !PUSH && tile + (int)gridDim.x >= num_tiles;
-            const uint32_t stage_base = (FUSED && last && ep.tma_store) ? u_base + (uint32_t)(half * 4 + quad) * 16384u : 0u;
+            // In the multi-GPU variant the same staged pieces are stored to every peer's output as well, so that tile
+            // needs neither the local round trip nor the push warps.
+            const bool last = tile + (int)gridDim.x >= num_tiles;
+            const bool staged = FUSED && last && ep.tma_store;
+            const uint32_t stage_base = staged ? u_base + (uint32_t)(half * 4 + quad) * 16384u : 0u;
             if (m0 + half * 128 < M)  // warp-uniform: otherwise this accumulator was not computed
-                wide_convert_columns<FUSED>(ep, &tmap_d, t_row, row, row_ok, a_add, half_a_mul, sb_add, sb_mul, n0, N, 0, TN,
-                                            stage_base, m0 + half * 128 + quad * 32, lane);
+                wide_convert_columns<FUSED>(ep, &tmap_d, peers.m, PUSH ? ep.n_peer : 0, t_row, row, row_ok, a_add, half_a_mul,
+                                            sb_add, sb_mul, n0, N, 0, TN, stage_base, m0 + half * 128 + quad * 32, lane);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tmem_empty);
             if (warp == kFirstEpi && lane == 0) QB_TRACE(3);
-            if (PUSH) {
+            if (PUSH && !staged) {
                 if (!mbar_wait(push_free + 8 * slot, slot_ph ^ 1u, 11)) *epi_abort = 1;  // all warps leave at the next tile's barrier
                 __threadfence_block();
                 __syncwarp();
@@ -933,6 +950,7 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             uint32_t local_tile = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+                if (FUSED && ep.tma_store && tile + (int)gridDim.x >= num_tiles) break;  // the epilogue warps send the last tile
                 const int m0 = (tile % tiles_m) * TM;
                 const int n0 = (tile / tiles_m) * TN;
                 const uint32_t slot = local_tile & 1u, slot_ph = (local_tile >> 1) & 1u;
@@ -1164,25 +1182,34 @@ static int pick_splits(int M, int N, int K, int sms) {
 }
 
 // Fused output D as bf16 [M, N] with row pitch ld: box = 64 columns (128 bytes, the swizzle span) x 32 rows, the piece one
-// warp of the 256 x 256 kernel stores at a time.  Returns false (and leaves ep->tma_store 0) where a tensor map cannot
-// describe the output: the kernel then keeps to per-thread stores.  QB200_GEMM_TMA_STORE=0 switches the bulk stores off.
-static bool make_output_map(CUtensorMap* map, EpilogueParams* ep, int M, int N) {
-    memset(map, 0, sizeof(*map));
-    ep->tma_store = 0;
-    if (ep->n_peer > 0 || !aligned16(ep->out) || ep->ld % 8 != 0) return false;
-    if (const char* e = getenv("QB200_GEMM_TMA_STORE"))
-        if (e[0] == '0') return false;
+// warp of the 256 x 256 kernel stores at a time; the same for every peer output of the multi-GPU variant.  Leaves
+// ep->tma_store 0 where a tensor map cannot describe an output: the kernel then keeps to per-thread stores (and push
+// warps).  QB200_GEMM_TMA_STORE=0 switches the bulk stores off.
+static int encode_output_map(CUtensorMap* map, void* base, long long ld, int M, int N) {
     EncodeTiledFn fn = get_encode_fn();
-    if (fn == nullptr) return false;
+    if (fn == nullptr) return QB200_ERR_DRIVER;
     const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
-    const cuuint64_t strides[1] = {(cuuint64_t)ep->ld * 2};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
     const cuuint32_t box[2] = {64, 32};
     const cuuint32_t estr[2] = {1, 1};
-    if (fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ep->out, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return false;
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS
+               ? QB200_OK : QB200_ERR_DRIVER;
+}
+
+template <bool PUSH>
+static void make_output_maps(CUtensorMap* map, PeerMaps<PUSH>* peers, EpilogueParams* ep, int M, int N) {
+    memset(map, 0, sizeof(*map));
+    memset(peers, 0, sizeof(*peers));
+    ep->tma_store = 0;
+    if (!aligned16(ep->out) || ep->ld % 8 != 0) return;
+    if (const char* e = getenv("QB200_GEMM_TMA_STORE"))
+        if (e[0] == '0') return;
+    if (PUSH != (ep->n_peer > 0)) return;
+    if (encode_output_map(map, ep->out, ep->ld, M, N) != QB200_OK) return;
+    for (int i = 0; PUSH && i < ep->n_peer; ++i)
+        if (!aligned16(ep->peer_out[i]) || encode_output_map(&peers->m[i], ep->peer_out[i], ep->ld, M, N) != QB200_OK) return;
     ep->tma_store = 1;
-    return true;
 }
 
 // A operand as int8 [rows, K] row-major; box = 128 bytes (one K stage, the swizzle span) x 256 rows.
@@ -1215,10 +1242,11 @@ static int launch_gemm_wide_a8(const EpilogueParams& ep_in, const void* a8, cons
     st = make_packed_map(&mb, b, N, K, wide::TN);
     if (st != QB200_OK) return st;
     CUtensorMap md;
-    make_output_map(&md, &ep, M, N);
+    PeerMaps<false> peers;
+    make_output_maps<false>(&md, &peers, &ep, M, N);
     const int tiles = ((M + wide::TM - 1) / wide::TM) * ((N + wide::TN - 1) / wide::TN);
     const int grid = tiles < sms ? tiles : sms;
-    kernel<<<grid, wide::kThreads - 32, wide::SMEM_BYTES, stream>>>(ma, mb, md, ep, M, N, K);
+    kernel<<<grid, wide::kThreads - 32, wide::SMEM_BYTES, stream>>>(ma, mb, md, peers, ep, M, N, K);
     return launch_status();
 }
 
@@ -1242,9 +1270,14 @@ static int launch_gemm_wide_impl(const EpilogueParams& ep_in, const void* a, con
     const int grid = tiles < sms ? tiles : sms;
     const int threads = PUSH ? wide::kThreads : wide::kThreads - 32 * wide::kPushWarps;
     CUtensorMap md;
-    if (FUSED && !PUSH) make_output_map(&md, &ep, M, N);
-    else memset(&md, 0, sizeof(md));
-    kernel<<<grid, threads, wide::SMEM_BYTES, stream>>>(ma, mb, md, ep, M, N, K);
+    PeerMaps<PUSH> peers;
+    if (FUSED) {
+        make_output_maps<PUSH>(&md, &peers, &ep, M, N);
+    } else {
+        memset(&md, 0, sizeof(md));
+        memset(&peers, 0, sizeof(peers));
+    }
+    kernel<<<grid, threads, wide::SMEM_BYTES, stream>>>(ma, mb, md, peers, ep, M, N, K);
     return launch_status();
 }
 

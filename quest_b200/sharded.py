@@ -62,12 +62,22 @@ class ShardedLinear4bit:
         self._ws = {}
 
     # -- compute for this rank's columns (CUDA kernels; overridden by the CPU tests of the host logic) --
+    _stage = None  # set by forward() while a caller wants to be told about stage boundaries
+
+    def sibling(self, w_shard: tuple[torch.Tensor, torch.Tensor, torch.Tensor]) -> "ShardedLinear4bit":
+        """Another layer of the same shape and sharding with its own weights that shares this layer's workspaces and
+        output buffers (layers of a model run one after the other; no new collective set-up is needed)."""
+        import copy
+        other = copy.copy(self)
+        other.w_int_packed, other.w_scale, other.w_add = w_shard
+        if other.w_int_packed.shape != self.w_int_packed.shape:
+            raise ValueError("a sibling layer must have this layer's shard shape")
+        return other
+
     def compute_shard(self, x: torch.Tensor, out_cols: torch.Tensor, ws: dict) -> None:
-        if self.use_hadamard:
-            quest.hadamard_quantize_int4(x, self.block, ws["a_int_packed"], ws["a_scale"], ws["a_int_row_sum"])
-        else:
-            quest.find_scale_int4(x, ws["a_scale"])
-            quest.quantize_int4(x, ws["a_scale"], None, ws["a_int_packed"], ws["a_int_row_sum"])
+        self.quantize_activations(x, ws)
+        if self._stage is not None:
+            self._stage("quantised")
         quest.fused_matmul_dequantize_int4_int4t_bf16_into(ws["a_int_packed"], self.w_int_packed, ws["a_int_row_sum"],
                                                            self.w_add, ws["a_scale"], self.w_scale, out_cols)
 
@@ -92,7 +102,11 @@ class ShardedLinear4bit:
             ptrs = [int(p) for p in hdl.buffer_ptrs]
             if len(ptrs) != self.world:
                 raise RuntimeError("symmetric memory group does not match the sharding world size")
-            out.append((t, hdl, ptrs))
+            try:  # every rank's buffer as a tensor in this process (used for the small-M exchange)
+                views = [hdl.get_buffer(r, (m, self.n_total), dtype) for r in range(self.world)]
+            except Exception:  # noqa: BLE001  (older symmetric-memory API: the push kernel handles every M)
+                views = None
+            out.append((t, hdl, ptrs, views))
         return out
 
     def workspaces(self, m: int, k: int, device, dtype) -> dict:
@@ -110,7 +124,12 @@ class ShardedLinear4bit:
             )
         return self._ws[key]
 
-    def forward(self, x: torch.Tensor, gather: bool = True) -> torch.Tensor:
+    SMALL_M = 16  # up to this many rows the single-GPU small-M kernels compute the shard and plain copies deliver it
+
+    def forward(self, x: torch.Tensor, gather: bool = True, on_stage=None) -> torch.Tensor:
+        """``on_stage(name)``, if given, is called after the activations are quantised ("quantised") and after this
+        rank's columns are computed and on their way ("computed"): a benchmark records events there."""
+        stage = on_stage if on_stage is not None else (lambda name: None)
         m, k = x.shape
         ws = self.workspaces(m, k, x.device, x.dtype)
         out = ws["out"]
@@ -121,19 +140,34 @@ class ShardedLinear4bit:
             self.compute_shard(x, out[:, self.n0:self.n1], ws)
             return out
         if self.exchange == "push":
-            t, hdl, ptrs = ws["symm"][ws["parity"]]
+            t, hdl, ptrs, views = ws["symm"][ws["parity"]]
             ws["parity"] ^= 1
             self.quantize_activations(x, ws)
-            off = self.n0 * t.element_size()
-            order = [self.rank] + [(self.rank + i) % self.world for i in range(1, self.world)]
-            quest.fused_matmul_dequantize_int4_int4t_bf16_push(
-                ws["a_int_packed"], self.w_int_packed, ws["a_int_row_sum"], self.w_add, ws["a_scale"], self.w_scale,
-                [ptrs[r] + off for r in order], self.n_total)
+            stage("quantised")
+            if m <= self.SMALL_M and views is not None:
+                # Few rows: the weight-streaming kernels (dp4a, split-K) are several times faster than a tensor-core
+                # tile kernel that walks K serially, and the block to deliver is tiny - compute it into the local buffer
+                # and copy it into every peer's.
+                mine = t[:, self.n0:self.n1]
+                quest.fused_matmul_dequantize_int4_int4t_bf16_into(ws["a_int_packed"], self.w_int_packed, ws["a_int_row_sum"],
+                                                                   self.w_add, ws["a_scale"], self.w_scale, mine)
+                for i in range(1, self.world):
+                    views[(self.rank + i) % self.world][:, self.n0:self.n1].copy_(mine)
+            else:
+                off = self.n0 * t.element_size()
+                order = [self.rank] + [(self.rank + i) % self.world for i in range(1, self.world)]
+                quest.fused_matmul_dequantize_int4_int4t_bf16_push(
+                    ws["a_int_packed"], self.w_int_packed, ws["a_int_row_sum"], self.w_add, ws["a_scale"], self.w_scale,
+                    [ptrs[r] + off for r in order], self.n_total)
+            stage("computed")
             hdl.barrier(channel=0)  # every rank's tiles have landed everywhere
             return t
         # NCCL all-gather wants one contiguous, equal-sized block per rank: gather [g, M, width], then
         # interleave the column blocks into the row-major [M, N_total] result.
+        self._stage = stage
         self.compute_shard(x, ws["local"][:, :self.n1 - self.n0], ws)
+        self._stage = None
+        stage("computed")
         dist.all_gather_into_tensor(ws["gathered"].view(-1), ws["local"].view(-1), group=self.group)
         if self.width_max * self.world == self.n_total:
             out.view(m, self.world, -1).copy_(ws["gathered"].permute(1, 0, 2))

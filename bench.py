@@ -165,29 +165,33 @@ def ev():
 
 def rotating_sets_time(make_call, n_sets: int, reps: int, dev) -> float:
     """Seconds per launch of a kernel, measured over back-to-back launches: ``make_call(i)`` launches it on operand set
-    i; the n_sets launches are captured once into a CUDA graph and the graph is replayed ``reps`` times between two
-    events on the launching stream.  The sets occupy distinct memory and together exceed the L2 size, so every launch
-    finds its operands in HBM, and no event or host gap sits between the launches."""
+    i; ``reps`` cycles through the n_sets sets are captured into ONE CUDA graph (at most 512 launches per graph, more are
+    covered by replaying it) and the graph is replayed between two events on the launching stream.  The sets occupy
+    distinct memory and together exceed the L2 size, so every launch finds its operands in HBM, and no event or host
+    gap sits between the launches."""
     make_call(0)  # first-call set-up (kernel attributes, scratch) outside the capture
     torch.cuda.synchronize()
+    cycles = max(1, min(reps, 512 // n_sets))
+    replays = max(1, -(-reps // cycles))
     side = torch.cuda.Stream(dev)
     side.wait_stream(torch.cuda.current_stream(dev))
     with torch.cuda.stream(side):
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=side):
-            for i in range(n_sets):
-                make_call(i)
+            for _ in range(cycles):
+                for i in range(n_sets):
+                    make_call(i)
     torch.cuda.current_stream(dev).wait_stream(side)
     for _ in range(2):
         graph.replay()
     torch.cuda.synchronize()
     e0, e1 = ev(), ev()
     e0.record()
-    for _ in range(reps):
+    for _ in range(replays):
         graph.replay()
     e1.record()
     torch.cuda.synchronize()
-    return e0.elapsed_time(e1) * 1e-3 / (reps * n_sets)
+    return e0.elapsed_time(e1) * 1e-3 / (replays * cycles * n_sets)
 
 
 def sets_for(bytes_per_set: float, cap_bytes: float = 6e9) -> int:
@@ -331,8 +335,24 @@ def run_b200(args):
             layer = ShardedLinear4bit((wp, ws, wa), n_total, rank, world, use_hadamard=True, block=args.block, exchange="nccl")
     flush = torch.zeros(L2_FLUSH_BYTES // 4, dtype=torch.int32, device=dev)
 
+    # One GPU: the layer takes the route linear_forward takes.  Where the library prefers it (256 x 256 GEMM kernel and a
+    # row length the tcgen05 quantiser tiles) the quantiser writes the GEMM's int8 operand instead of packed int4.
+    use_a8 = world == 1 and args.block in (64, 128, 256) and k % args.block == 0 and quest.prefers_a8(m, k, n_local)
     a_scale = torch.empty(m, 1, dtype=torch.bfloat16, device=dev)
-    a_packed = torch.empty(m, k // 2, dtype=torch.uint8, device=dev)
+    a_packed = torch.empty(m, k if use_a8 else k // 2, dtype=torch.uint8, device=dev)
+
+    def f1_op(x_, codes, sc_, rs_):
+        if use_a8:
+            quest.hadamard_quantize_a8(x_, args.block, codes, sc_, rs_)
+        else:
+            quest.hadamard_quantize_int4(x_, args.block, codes, sc_, rs_)
+
+    def gemm_op(codes, w_, rs_, sc_, out_):
+        if use_a8:
+            quest.fused_matmul_dequantize_a8(codes, w_, rs_, wa, sc_, ws, out_)
+        else:
+            quest.fused_matmul_dequantize_int4_int4t_bf16(codes, w_, rs_, wa, sc_, ws, out_)
+
     a_rsum = torch.empty(m, 1, dtype=torch.int32, device=dev)
     out = torch.empty(m, n_local, dtype=torch.bfloat16, device=dev)
 
@@ -353,17 +373,17 @@ def run_b200(args):
 
         if args.workload == "hadamard_quantize":
             e0.record()
-            quest.hadamard_quantize_int4(x, args.block, a_packed, a_scale, a_rsum)
+            f1_op(x, a_packed, a_scale, a_rsum)
             mark(e1); mark(e2); e3.record()
         elif args.workload == "gemm":
             e0.record(); mark(e1)
-            quest.fused_matmul_dequantize_int4_int4t_bf16(a_packed, wp, a_rsum, wa, a_scale, ws, out)
+            gemm_op(a_packed, wp, a_rsum, a_scale, out)
             mark(e2); e3.record()
         elif world == 1:
             e0.record()
-            quest.hadamard_quantize_int4(x, args.block, a_packed, a_scale, a_rsum)
+            f1_op(x, a_packed, a_scale, a_rsum)
             mark(e1)
-            quest.fused_matmul_dequantize_int4_int4t_bf16(a_packed, wp, a_rsum, wa, a_scale, ws, out)
+            gemm_op(a_packed, wp, a_rsum, a_scale, out)
             mark(e2); e3.record()
         else:  # N > 1: the sharded layer (push: the GEMM epilogue stores its tiles into every rank's output, then one
             # device-side barrier; nccl: all-gather + interleaving copy); events at the layer's two stage boundaries
@@ -374,7 +394,7 @@ def run_b200(args):
             timers.append((e0, e1 if split else e0, e2 if split else e3, e3))
 
     if args.workload == "gemm":  # the GEMM-only workload needs quantised activations once
-        quest.hadamard_quantize_int4(x, args.block, a_packed, a_scale, a_rsum)
+        f1_op(x, a_packed, a_scale, a_rsum)
 
     def barrier():
         if world > 1:
@@ -394,8 +414,8 @@ def run_b200(args):
         with torch.cuda.stream(side):
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=side):
-                quest.hadamard_quantize_int4(x, args.block, a_packed, a_scale, a_rsum)
-                quest.fused_matmul_dequantize_int4_int4t_bf16(a_packed, wp, a_rsum, wa, a_scale, ws, out)
+                f1_op(x, a_packed, a_scale, a_rsum)
+                gemm_op(a_packed, wp, a_rsum, a_scale, out)
         torch.cuda.current_stream().wait_stream(side)
         for _ in range(3):
             graph.replay()
@@ -407,40 +427,41 @@ def run_b200(args):
     # Timed region 1: the K steps the headline value comes from.
     # One GPU: exactly K steps back to back between two events, step i on operand set i mod n; the n sets (activations,
     # workspaces, a copy of the weights, output) occupy distinct memory and together exceed 2.5 x L2, so every step finds
-    # its inputs in HBM.  The n steps are captured once into a CUDA graph that is replayed K // n times; the K % n
-    # remaining steps are launched one by one inside the same bracket.
+    # its inputs in HBM.  Up to 256 consecutive steps are captured once into a CUDA graph (K itself for short runs), the
+    # graph is replayed as often as it fits into K and the remaining steps are launched one by one inside the same bracket.
     timers = []
     t_step_b2b = None
     wall0 = time.perf_counter()
     if graph is not None:
-        set_bytes = 2.0 * m * k + m * k / 2 + n_local * k / 2 + 2.0 * m * n_local
+        set_bytes = 2.0 * m * k + a_packed.numel() + n_local * k / 2 + 2.0 * m * n_local
         n_sets = min(sets_for(set_bytes), max(args.steps, 1))
         lsets = [(x.clone(), torch.empty_like(a_packed), torch.empty_like(a_scale), torch.empty_like(a_rsum), wp.clone(),
                   torch.empty_like(out)) for _ in range(n_sets)]
 
         def layer_step(i):
             xs, pk, sc, rs, wps, os_ = lsets[i]
-            quest.hadamard_quantize_int4(xs, args.block, pk, sc, rs)
-            quest.fused_matmul_dequantize_int4_int4t_bf16(pk, wps, rs, wa, sc, ws, os_)
+            f1_op(xs, pk, sc, rs)
+            gemm_op(pk, wps, rs, sc, os_)
 
         side = torch.cuda.Stream(dev)
         side.wait_stream(torch.cuda.current_stream())
+        chain_steps = min(args.steps, max(n_sets, 256 // n_sets * n_sets))  # steps per graph: K itself for short runs
         with torch.cuda.stream(side):
             chain = torch.cuda.CUDAGraph()
             with torch.cuda.graph(chain, stream=side):
-                for i in range(n_sets):
-                    layer_step(i)
+                for i in range(chain_steps):
+                    layer_step(i % n_sets)
         torch.cuda.current_stream().wait_stream(side)
-        for _ in range(max(2, -(-3 // n_sets))):  # at least 3 more warm-up steps through the timed path
+        for _ in range(max(2, -(-3 // chain_steps))):  # at least 3 more warm-up steps through the timed path
             chain.replay()
         torch.cuda.synchronize()
         e0, e3 = ev(), ev()
         wall0 = time.perf_counter()
         e0.record()
-        for _ in range(args.steps // n_sets):
+        for _ in range(args.steps // chain_steps):
             chain.replay()
-        for i in range(args.steps % n_sets):
-            layer_step(i)
+        for i in range(args.steps % chain_steps):
+            layer_step(i % n_sets)
         e3.record()
         barrier()
         t_step_b2b = e0.elapsed_time(e3) * 1e-3 / args.steps
@@ -494,22 +515,21 @@ def run_b200(args):
     t_gemm_b2b = t_f1_b2b = None
     n_gemm_sets = n_f1_sets = 0
     if args.workload in ("linear", "gemm"):
-        gemm_set_bytes = m * k / 2 + n_local * k / 2 + 2.0 * m * n_local
+        gemm_set_bytes = a_packed.numel() + n_local * k / 2 + 2.0 * m * n_local
         n_gemm_sets = sets_for(gemm_set_bytes)
-        quest.hadamard_quantize_int4(x, args.block, a_packed, a_scale, a_rsum)
+        f1_op(x, a_packed, a_scale, a_rsum)
         gsets = [(a_packed.clone(), wp.clone(), torch.empty_like(out)) for _ in range(n_gemm_sets)]
         reps = max(1, -(-args.steps // n_gemm_sets))
         t_gemm_b2b = rotating_sets_time(
-            lambda i: quest.fused_matmul_dequantize_int4_int4t_bf16(gsets[i][0], gsets[i][1], a_rsum, wa, a_scale, ws, gsets[i][2]),
-            n_gemm_sets, reps, dev)
+            lambda i: gemm_op(gsets[i][0], gsets[i][1], a_rsum, a_scale, gsets[i][2]), n_gemm_sets, reps, dev)
         del gsets
     if args.workload in ("linear", "hadamard_quantize"):
-        f1_set_bytes = 2.5 * m * k
+        f1_set_bytes = 2.0 * m * k + a_packed.numel()
         n_f1_sets = sets_for(f1_set_bytes)
         fsets = [(x.clone(), torch.empty_like(a_packed)) for _ in range(n_f1_sets)]
         reps = max(1, -(-args.steps // n_f1_sets))
         t_f1_b2b = rotating_sets_time(
-            lambda i: quest.hadamard_quantize_int4(fsets[i][0], args.block, fsets[i][1], a_scale, a_rsum), n_f1_sets, reps, dev)
+            lambda i: f1_op(fsets[i][0], fsets[i][1], a_scale, a_rsum), n_f1_sets, reps, dev)
         del fsets
     # The fused quantiser on an input far larger than L2 (M=65536, K=8192: 1.07 GB in, 0.27 GB out), single GPU only.
     f1_large = None
@@ -572,8 +592,8 @@ def run_b200(args):
         def e2e_step():
             x_dev.copy_(x_pin, non_blocking=True)
             if world == 1:
-                y = quest.linear_forward(x_dev, wp, ws, wa, out=out, _a_scale=a_scale, _a_int_packed=a_packed,
-                                         _a_int_row_sum=a_rsum, use_hadamard=True, block=args.block)
+                y = quest.linear_forward(x_dev, wp, ws, wa, out=out, _a_scale=a_scale, _a_int_row_sum=a_rsum, use_hadamard=True,
+                                         block=args.block, **({"_a_int8": a_packed} if use_a8 else {"_a_int_packed": a_packed}))
             else:
                 y = layer(x_dev)
             y_pin.copy_(y, non_blocking=True)
@@ -626,8 +646,8 @@ def run_b200(args):
                     flush.add_(1)
                     if world == 1:
                         sc, pk, rs = wsb[b]
-                        quest.linear_forward(xb[b], wp, ws, wa, out=ob[b], _a_scale=sc, _a_int_packed=pk, _a_int_row_sum=rs,
-                                             use_hadamard=True, block=args.block)
+                        quest.linear_forward(xb[b], wp, ws, wa, out=ob[b], _a_scale=sc, _a_int_row_sum=rs, use_hadamard=True,
+                                             block=args.block, **({"_a_int8": pk} if use_a8 else {"_a_int_packed": pk}))
                     else:
                         ob[b].copy_(layer(xb[b]))
                     cmp_done[b] = torch.cuda.Event(); cmp_done[b].record(s_cmp)
@@ -662,7 +682,7 @@ def run_b200(args):
     if rank == 0:
         ops_total = 2.0 * m * n_total * k
         ops_gemm = 2.0 * m * n_local * k
-        f1_bytes = 2.0 * m * k + m * k / 2 + 6.0 * m  # bf16 in + packed out + bf16 scale + int32 row sum
+        f1_bytes = 2.0 * m * k + a_packed.numel() + 6.0 * m  # bf16 in + codes out (packed int4, or the int8 operand) + bf16 scale + int32 row sum
         int8_peak = 2.0 * peaks["bf16_tflops"]        # tcgen05 kind::i8 runs at twice the bf16 rate
         gemm_traffic = NCU_TRAFFIC.get(("gemm", m, k, n_local))
         f1_traffic = NCU_TRAFFIC.get(("hadamard_quantize", m, k))
@@ -691,7 +711,10 @@ def run_b200(args):
                          "traffic_source": gemm_traffic[1] if gemm_traffic else None,
                          "us_per_launch": t_gemm_roof * 1e6,
                          "us_per_launch_isolated": t_gemm * 1e6 if t_gemm > 0 else None,
-                         "timing": b2b_note.format(n=n_gemm_sets, mb=n_gemm_sets * (m * k / 2 + n_local * k / 2 + 2.0 * m * n_local) / 1e6)
+                         "route": ("int8 operand: the quantiser writes 16 x code as int8 in the GEMM's operand order, the 256x256 kernel copies A"
+                                   " with TMA and unpacks only B (the library's default where both kernels apply; QB200_A8=0 for packed A)")
+                         if use_a8 else "packed int4 A and B, both unpacked in the kernel",
+                         "timing": b2b_note.format(n=n_gemm_sets, mb=n_gemm_sets * (a_packed.numel() + n_local * k / 2 + 2.0 * m * n_local) / 1e6)
                          if t_gemm_b2b else "events between the step's kernels",
                          "isolated_note": "us_per_launch_isolated: one launch between two events inside the step, launch gap included"},
             "roofline_hadamard_quantize": {"kernel": "fused Hadamard+scale+quantise+pack: hadamard_quant_tc_kernel (tcgen05) for large inputs,"
@@ -705,7 +728,8 @@ def run_b200(args):
                                            "us_per_launch": t_f1_roof * 1e6,
                                            "us_per_launch_isolated": t_f1 * 1e6 if t_f1 > 0 else None,
                                            "algorithmic_bytes": f1_bytes,
-                                           "timing": b2b_note.format(n=n_f1_sets, mb=n_f1_sets * 2.5 * m * k / 1e6)
+                                           "output": "int8 operand [M, K] (see roofline.route)" if use_a8 else "packed int4 [M, K/2]",
+                                           "timing": b2b_note.format(n=n_f1_sets, mb=n_f1_sets * (2.0 * m * k + a_packed.numel()) / 1e6)
                                            if t_f1_b2b else "events between the step's kernels"},
             "e2e": e2e,
             "gpu_launches": launches_per_step * args.steps,
@@ -958,9 +982,9 @@ def run_sweep(args):
             t_g = rotating_sets_time(lambda i: quest.fused_matmul_dequantize_int4_int4t_bf16(sets[i][1], sets[i][2], rs, wa, sc, ws, sets[i][3]),
                                      ns, reps, dev)
 
-            def both(i):
-                quest.hadamard_quantize_int4(sets[i][0], 128, sets[i][1], sc, rs)
-                quest.fused_matmul_dequantize_int4_int4t_bf16(sets[i][1], sets[i][2], rs, wa, sc, ws, sets[i][3])
+            def both(i):  # the layer as linear_forward runs it (one library call with a dependent launch up to 16 rows)
+                quest.linear_forward(sets[i][0], sets[i][2], ws, wa, out=sets[i][3], _a_scale=sc, _a_int_packed=sets[i][1],
+                                     _a_int_row_sum=rs, use_hadamard=True)
             t_l = rotating_sets_time(both, ns, reps, dev)
             ops = 2.0 * m * n * 4096
             linear.append({"M": m, "N": n, "K": 4096, "quantize_us": t_q * 1e6, "gemm_us": t_g * 1e6, "layer_us": t_l * 1e6,

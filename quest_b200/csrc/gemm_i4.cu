@@ -1501,7 +1501,7 @@ extern "C" int fused_matmul_dequantize_a8_int4t_bf16_cuda(void* mat_d, const voi
     return launch_gemm_wide_a8(ep, mat_a8, mat_b, M, K, N, sms, dev, stream);
 }
 
-constexpr bool kA8ByDefault = false;  // the route is chosen only on request (QB200_A8=1) until it measures faster everywhere
+constexpr bool kA8ByDefault = true;  // measured faster wherever the 256 x 256 kernel and the tcgen05 quantiser both apply (QB200_A8=0 switches it off)
 
 // 1 if, for this layer shape, the int8-operand route (hadamard_quantize_a8_cuda_bf16 + the GEMM above) is the faster one:
 // the 256 x 256 kernel would be chosen anyway and the quantiser's tcgen05 kernel can tile K.
@@ -1539,6 +1539,24 @@ extern "C" int fused_matmul_dequantize_int4_int4t_bf16_cuda(void* mat_d, const v
                                                             int N, cudaStream_t stream) {
     return fused_matmul_dequantize_int4_int4t_bf16_strided_cuda(mat_d, (long long)N, mat_a, mat_b, vec_a_add, vec_b_add,
                                                                 vec_a_mul, vec_b_mul, M, K, N, stream);
+}
+
+extern "C" int hadamard_quantize_int4_cuda_bf16(void*, void*, void*, const void*, int, int, int, cudaStream_t);
+
+extern "C" int w4a4_linear_hadamard_bf16_cuda(void* mat_d, const void* x, const void* w_int_packed, const void* w_add,
+                                              const void* w_scale, void* a_int_packed, void* a_scale, void* a_int_row_sum,
+                                              int M, int K, int N, int block, cudaStream_t stream) {
+    if (!a_int_row_sum) return QB200_ERR_INVALID_ARGUMENT;
+    const int st = hadamard_quantize_int4_cuda_bf16(a_int_packed, a_scale, a_int_row_sum, x, K, M, block, stream);
+    if (st != QB200_OK) return st;
+    // Up to 16 rows the GEMM is the weight-streaming dp4a kernel, whose prologue (the first weights of every warp) does
+    // not depend on the activations: it is launched with a programmatic dependency, starts while the quantiser still
+    // runs and waits for it on the device.  Larger shapes take the ordinary, fully ordered launch.
+    tl_dependent_launch = true;
+    const int st2 = fused_matmul_dequantize_int4_int4t_bf16_cuda(mat_d, a_int_packed, w_int_packed, a_int_row_sum, w_add,
+                                                                 a_scale, w_scale, M, K, N, stream);
+    tl_dependent_launch = false;
+    return st2;
 }
 
 extern "C" int quest_b200_test_bounded_wait_cuda(void* mat_d, const void* mat_a, const void* mat_b, const void* vec_a_add,

@@ -13,6 +13,10 @@
 // Replaces, for these shapes, gemm-quest/quest/matmul_kernel.cu:8-63 and fused_matmul_dequantize_kernel.cu:4-57.
 #pragma once
 
+// Set (per host thread) by the fused layer entry point around its GEMM call: the small-M kernel is then launched with
+// a programmatic dependency on the preceding kernel of the stream instead of a full one.
+static thread_local bool tl_dependent_launch = false;
+
 namespace gemv {
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
@@ -49,6 +53,9 @@ gemv_i4_kernel(const uint8_t* __restrict__ A, const uint8_t* __restrict__ B, con
     int group = blockIdx.x * gemv::kWarps + warp;
     uint4 wcur[C];
     load_weights(wcur, group * C, group < groups ? lane : chunks);
+    // Launched with a programmatic dependency on the kernel that quantises the activations (fused layer call), this
+    // grid starts while that kernel still runs: everything up to here touches only the weights.  Now wait for it.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     for (int i = threadIdx.x; i < MR * chunks; i += gemv::kThreads) {
         const int r = i / chunks, ch = i - r * chunks;
         gemv_sA[i] = r < M ? *reinterpret_cast<const uint4*>(A + (size_t)r * row_bytes + (size_t)ch * 16) : make_uint4(0, 0, 0, 0);
@@ -148,7 +155,20 @@ static int launch_gemv(const EpilogueParams& ep, const void* a, const void* b, i
     int grid = (groups + gemv::kWarps - 1) / gemv::kWarps;
     const int per_sm = smem > 100 * 1024 ? 1 : (smem > 48 * 1024 ? 2 : 4);
     if (grid > sms * per_sm) grid = sms * per_sm;
-    kernel<<<grid, gemv::kThreads, smem, stream>>>(static_cast<const uint8_t*>(a), static_cast<const uint8_t*>(b), ep, M, N, K);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(gemv::kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = tl_dependent_launch ? 1 : 0;  // the fused layer call: start behind the quantiser without waiting for its end
+    if (cudaLaunchKernelEx(&cfg, kernel, static_cast<const uint8_t*>(a), static_cast<const uint8_t*>(b), ep, M, N, K) != cudaSuccess) {
+        cudaGetLastError();
+        return QB200_ERR_CUDA;
+    }
     return launch_status();
 }
 

@@ -366,6 +366,9 @@ hadamard_quant_mma_kernel(const RowParams p, const int W, const int G, const int
         atomicMax(&g_hq_trace[1], t);
     }
 #endif
+    // A kernel launched behind this one with a programmatic dependency (the small-M GEMM of the fused layer call) may
+    // start its own prologue now; it waits for this grid's results itself.  Without such a dependent this does nothing.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const int grp = warp / W;      // row group of this warp

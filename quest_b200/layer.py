@@ -16,6 +16,7 @@ import quest_b200 as quest
 from .workspace import default_cache
 
 HADAMARD_BLOCK = 128  # the reference hard-codes block 128 (utils.py:17, 39, 90)
+SMALL_M_ONE_CALL = 16  # up to this many rows linear_forward makes ONE library call for the whole layer
 
 
 def preprocess_weight(
@@ -119,6 +120,10 @@ def linear_forward(
                                          vec_a_mul=a_scale, vec_b_mul=w_scale, out=out)
         return out
     a_int_packed = torch.empty(M, K // 2, dtype=torch.uint8, device=device) if _a_int_packed is None else _a_int_packed
+    if use_hadamard and not debug_mode and M <= SMALL_M_ONE_CALL and out.is_contiguous():
+        # few rows: one library call; the weight-streaming GEMM starts behind the quantiser with a dependent launch
+        return quest.w4a4_linear_hadamard(activation, w_int_packed, w_add, w_scale, out, a_int_packed, a_scale, a_int_row_sum,
+                                          block=block)
     if use_hadamard:
         quest.hadamard_quantize_int4(activation, block=block, x_int_packed=a_int_packed, scale=a_scale,
                                      x_int_row_sum=a_int_row_sum)

@@ -335,3 +335,40 @@ def test_prefill_fused_blocks_track_the_unfused_model():
     assert rel < 0.02, rel
     eager_ms, graph_ms, y_graph = prefill_time(b, 4, 64, n_warmup=2, n_iter=3, seed=1)
     assert y_graph.equal(yb)
+
+
+# ------------------------------------------------------------------ the layer in one call (few rows) ---
+@pytest.mark.parametrize("m", [1, 3, 16])
+@pytest.mark.parametrize("k,n", [(4096, 4096), (5632, 2048), (8192, 1280)])
+def test_one_call_layer_equals_the_two_op_route(m, k, n):
+    """Up to 16 rows linear_forward makes one library call whose GEMM kernel is launched with a programmatic dependency
+    on the quantiser: the workspaces and the output must hold exactly what the two ops called one after the other
+    give, call after call, and also when the call is replayed from a CUDA graph."""
+    x = make_activations("student", m, k, seed=m + k).to(DEV)
+    w = (0.02 * torch.randn(n, k, generator=torch.Generator().manual_seed(n))).to(torch.bfloat16).to(DEV)
+    wp, ws, wa, _ = quest.preprocess_weight(w, use_hadamard=True)
+    p_ref, s_ref, r_ref = quest.hadamard_quantize_int4(x)
+    y_ref = quest.fused_matmul_dequantize_int4_int4t_bf16(p_ref, wp, r_ref, wa, s_ref, ws)
+    pk = torch.zeros(m, k // 2, dtype=torch.uint8, device=DEV)
+    sc = torch.zeros(m, 1, dtype=torch.bfloat16, device=DEV)
+    rs = torch.zeros(m, 1, dtype=torch.int32, device=DEV)
+    out = torch.zeros(m, n, dtype=torch.bfloat16, device=DEV)
+    for _ in range(3):
+        out.zero_()
+        y = quest.linear_forward(x, wp, ws, wa, out=out, _a_scale=sc, _a_int_packed=pk, _a_int_row_sum=rs, use_hadamard=True)
+        assert y is out and out.equal(y_ref) and pk.equal(p_ref) and sc.equal(s_ref) and rs.equal(r_ref)
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        quest.linear_forward(x, wp, ws, wa, out=out, _a_scale=sc, _a_int_packed=pk, _a_int_row_sum=rs, use_hadamard=True)
+    torch.cuda.current_stream().wait_stream(s)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        quest.linear_forward(x, wp, ws, wa, out=out, _a_scale=sc, _a_int_packed=pk, _a_int_row_sum=rs, use_hadamard=True)
+    x2 = make_activations("randn", m, k, seed=7).to(DEV)
+    x.copy_(x2)
+    out.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    p2, s2, r2 = quest.hadamard_quantize_int4(x2)
+    assert out.equal(quest.fused_matmul_dequantize_int4_int4t_bf16(p2, wp, r2, wa, s2, ws)) and pk.equal(p2)

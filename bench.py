@@ -42,10 +42,15 @@ L2_BYTES = 126 << 20
 # DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture), keyed by kernel and launch
 # shape; the file under profiles/ holds the capture's command and figures.  Only these shapes report `traffic`.
 NCU_TRAFFIC = {
-    ("gemm", 2048, 4096, 4096): (12.67e6 + 2.0 * 2048 * 4096, "profiles/gemm_i4_wide_kernel_fused_m2048_k4096_n4096.md: 12.67 MB read by "
-                                 "the kernel; its 16.78 MB of output are still in L2 when it ends and are written back afterwards"),
-    ("hadamard_quantize", 2048, 4096): (16.81e6 + 2048 * 4096 / 2 + 6.0 * 2048, "profiles/hadamard_quant_mma_kernel_m16384_k4096.md, scaled "
-                                        "by rows: the input is read exactly once, outputs are written back after the kernel"),
+    # (kernel, M, K, N or None, int8-operand route?)
+    ("gemm", 2048, 4096, 4096, True): (16.86e6 + 2.0 * 2048 * 4096, "profiles/gemm_i4_wide_kernel_fused_m2048_k4096_n4096.md (A8 column): 16.86 MB"
+                                       " read by the kernel; its 16.78 MB of output are still in L2 when it ends and are written back afterwards"),
+    ("gemm", 2048, 4096, 4096, False): (12.67e6 + 2.0 * 2048 * 4096, "profiles/gemm_i4_wide_kernel_fused_m2048_k4096_n4096.md (packed column): 12.67 MB"
+                                        " read by the kernel; its 16.78 MB of output are still in L2 when it ends and are written back afterwards"),
+    ("hadamard_quantize", 2048, 4096, None, True): (16.82e6 + 2048 * 4096 + 6.0 * 2048, "profiles/hadamard_quant_kernels_headline_and_large.md (first"
+                                                    " column): the input is read exactly once, the outputs are written back after the kernel"),
+    ("hadamard_quantize", 2048, 4096, None, False): (16.81e6 + 2048 * 4096 / 2 + 6.0 * 2048, "profiles/hadamard_quant_kernels_headline_and_large.md"
+                                                     " (second column): the input is read exactly once, the outputs are written back after the kernel"),
 }
 
 
@@ -586,7 +591,11 @@ def run_b200(args):
     e2e = None
     if not args.no_e2e and args.workload == "linear":
         x_pin = x_host.pin_memory()
-        y_pin = torch.empty(m, n_total, dtype=torch.bfloat16).pin_memory()
+        # N > 1: every rank copies the (replicated) activations in; the assembled [M, N_total] result goes back to the
+        # host ONCE, split by rows over the ranks' PCIe links (rank r reads rows r*M/N .. of its own assembled copy).
+        rows_per_rank = -(-m // world)
+        r0, r1 = min(m, rank * rows_per_rank), min(m, (rank + 1) * rows_per_rank)
+        y_pin = torch.empty(r1 - r0, n_total, dtype=torch.bfloat16).pin_memory()
         x_dev = torch.empty_like(x)
 
         def e2e_step():
@@ -595,7 +604,7 @@ def run_b200(args):
                 y = quest.linear_forward(x_dev, wp, ws, wa, out=out, _a_scale=a_scale, _a_int_row_sum=a_rsum, use_hadamard=True,
                                          block=args.block, **({"_a_int8": a_packed} if use_a8 else {"_a_int_packed": a_packed}))
             else:
-                y = layer(x_dev)
+                y = layer(x_dev)[r0:r1]
             y_pin.copy_(y, non_blocking=True)
 
         for _ in range(3):
@@ -626,9 +635,9 @@ def run_b200(args):
         # private staging buffer (inside the timed region) and the copy-out stream reads that.
         s_in, s_cmp, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
         xb = [torch.empty_like(x) for _ in range(2)]
-        ob = [torch.empty(m, n_total, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+        ob = [torch.empty(r1 - r0, n_total, dtype=torch.bfloat16, device=dev) for _ in range(2)]
         wsb = [(torch.empty_like(a_scale), torch.empty_like(a_packed), torch.empty_like(a_rsum)) for _ in range(2)]
-        yb = [torch.empty(m, n_total, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+        yb = [torch.empty(r1 - r0, n_total, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
         cmp_done, out_done = [None, None], [None, None]
 
         def pipelined(nsteps):
@@ -649,7 +658,7 @@ def run_b200(args):
                         quest.linear_forward(xb[b], wp, ws, wa, out=ob[b], _a_scale=sc, _a_int_row_sum=rs, use_hadamard=True,
                                              block=args.block, **({"_a_int8": pk} if use_a8 else {"_a_int_packed": pk}))
                     else:
-                        ob[b].copy_(layer(xb[b]))
+                        ob[b].copy_(layer(xb[b])[r0:r1])
                     cmp_done[b] = torch.cuda.Event(); cmp_done[b].record(s_cmp)
                 with torch.cuda.stream(s_out):
                     s_out.wait_event(cmp_done[b])
@@ -672,7 +681,8 @@ def run_b200(args):
         e2e = {"value": 2.0 * m * n_total * k / t_pipe / 1e12, "unit": "TOPS", "ms_per_step": t_pipe * 1e3,
                "h2d_bytes_per_step": x_pin.numel() * 2, "d2h_bytes_per_step": y_pin.numel() * 2, "api": api, "steps": n_e2e,
                "mode": "three streams (copy in / layer / copy out), two buffer sets; L2 flushed before every layer call"
-                       + ("; every rank copies the activations in and the full assembled [M, N_total] result out" if world > 1 else ""),
+                       + ("; every rank copies the activations in; the assembled [M, N_total] result is read back once, split by rows over"
+                          " the ranks (h2d/d2h bytes are per rank)" if world > 1 else ""),
                "one_stream": one_stream}
 
     status = quest.device_status()
@@ -684,8 +694,8 @@ def run_b200(args):
         ops_gemm = 2.0 * m * n_local * k
         f1_bytes = 2.0 * m * k + a_packed.numel() + 6.0 * m  # bf16 in + codes out (packed int4, or the int8 operand) + bf16 scale + int32 row sum
         int8_peak = 2.0 * peaks["bf16_tflops"]        # tcgen05 kind::i8 runs at twice the bf16 rate
-        gemm_traffic = NCU_TRAFFIC.get(("gemm", m, k, n_local))
-        f1_traffic = NCU_TRAFFIC.get(("hadamard_quantize", m, k))
+        gemm_traffic = NCU_TRAFFIC.get(("gemm", m, k, n_local, bool(use_a8)))
+        f1_traffic = NCU_TRAFFIC.get(("hadamard_quantize", m, k, None, bool(use_a8)))
         t_gemm_roof = t_gemm_b2b if t_gemm_b2b else t_gemm
         t_f1_roof = t_f1_b2b if t_f1_b2b else t_f1
         if args.workload == "hadamard_quantize":

@@ -713,7 +713,7 @@ def run_b200(args):
             "vs_baseline": None, "dtype": "int4 operands, int8 tcgen05 MMA, int32 accumulate, bf16 out",
             "data": "synthetic", "config": workload_config(args, world),
             "roofline": {"kernel": "gemm_i4_wide_kernel / gemm_i4_kernel (TMA -> int4 unpack -> tcgen05 kind::i8, fused dequant epilogue;"
-                                   " 256x256 tiles at the default shape)", "bound": "tensor",
+                                   " 256x256 tiles at the default shape, last tile of a CTA stored with bulk tensor stores)", "bound": "tensor",
                          "achieved": ops_gemm / t_gemm_roof / 1e12 if t_gemm_roof > 0 else None, "peak": int8_peak,
                          "unit": "TOPS", "frac": (ops_gemm / t_gemm_roof / 1e12) / int8_peak if t_gemm_roof > 0 else None,
                          "peak_source": f"2 x bf16_tflops ({peaks['bf16_tflops']}) of {peaks['source']}",
@@ -727,8 +727,10 @@ def run_b200(args):
                          "timing": b2b_note.format(n=n_gemm_sets, mb=n_gemm_sets * (a_packed.numel() + n_local * k / 2 + 2.0 * m * n_local) / 1e6)
                          if t_gemm_b2b else "events between the step's kernels",
                          "isolated_note": "us_per_launch_isolated: one launch between two events inside the step, launch gap included"},
-            "roofline_hadamard_quantize": {"kernel": "fused Hadamard+scale+quantise+pack: hadamard_quant_tc_kernel (tcgen05) for large inputs,"
-                                                     " hadamard_quant_mma_kernel below (see DESIGN.md for the crossover)", "bound": "hbm",
+            "roofline_hadamard_quantize": {"kernel": ("fused Hadamard+scale+quantise: hadamard_quant_tc_kernel (tcgen05), writing the GEMM's int8 operand"
+                                                      if use_a8 else
+                                                      "fused Hadamard+scale+quantise+pack: hadamard_quant_tc_kernel (tcgen05) from ~12 M elements,"
+                                                      " hadamard_quant_mma_kernel below and for row lengths the tcgen05 tiling refuses"), "bound": "hbm",
                                            "achieved": f1_bytes / t_f1_roof / 1e9 if t_f1_roof > 0 else None,
                                            "peak": peaks["hbm_gbs"], "unit": "GB/s",
                                            "frac": (f1_bytes / t_f1_roof / 1e9) / peaks["hbm_gbs"] if t_f1_roof > 0 else None,

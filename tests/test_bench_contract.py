@@ -39,3 +39,16 @@ def test_other_ranks_of_the_reference_arm_exit_quietly():
                           "--steps", "1", "--warmup", "0", "--m", "64", "--k", "256", "--n", "64"],
                          capture_output=True, text=True, timeout=300, cwd=ROOT, env=env)
     assert res.returncode == 0 and res.stdout.strip() == ""
+
+
+def test_operand_set_counts_keep_launches_cold_and_graphs_small():
+    """sets_for(): enough operand sets that consecutive launches cannot find their inputs in L2 (2.5 x L2 in total), two
+    for a set that is larger than L2 by itself, never more than 256 launches per graph or 6 GB of copies."""
+    sys.path.insert(0, ROOT)
+    import bench
+    l2 = bench.L2_BYTES
+    assert bench.sets_for(2 * l2) == 2
+    n = bench.sets_for(29.4e6)                      # the headline GEMM's operands
+    assert n * 29.4e6 >= 2.5 * l2 and n <= 16
+    assert bench.sets_for(10e3) == 256              # tiny sets: capped (they stay L2-resident, and say so)
+    assert bench.sets_for(1.5e9) * 1.5e9 <= 6e9 + 1.5e9

@@ -631,3 +631,12 @@ def test_linear_forward_takes_the_int8_operand_route_where_preferred(monkeypatch
     assert y_a8.equal(y_packed)
     monkeypatch.delenv("QB200_A8")
     assert not quest.prefers_a8(16, k, n) and not quest.prefers_a8(m, 5632, n)
+    # the library's own choice at this shape is the int8-operand route; a caller's packed workspace keeps the packed one
+    assert quest.prefers_a8(m, k, n)
+    assert quest.linear_forward(x, wp, ws, wa, use_hadamard=True).equal(y_packed)
+    pk = torch.empty(m, k // 2, dtype=torch.uint8, device=DEV)
+    assert quest.linear_forward(x, wp, ws, wa, use_hadamard=True, _a_int_packed=pk).equal(y_packed)
+    assert pk.equal(quest.hadamard_quantize_int4(x)[0])
+    # and the module (workspaces from the shared cache) gives the same bits, call after call
+    lin = quest.Linear4bit(k, n, bias=False, device=DEV, dtype=torch.bfloat16, use_hadamard=True, weight=w)
+    assert lin(x).equal(y_packed) and lin(x).equal(y_packed)

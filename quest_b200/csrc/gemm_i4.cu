@@ -96,6 +96,9 @@ struct EpilogueParams {
     int* counters;          // one per output tile, all zero between launches
     int tma_store;          // 256 x 256 kernel, fused: the output tensor map is valid (the last tile leaves as bulk tensor stores)
     int test_skip_producer; // tests only: the TMA producer issues nothing, so that every bounded wait of the launch runs out
+    // 256-row kernel: the N range is cut into col_count tile columns whose widths are multiples of 16, at most 256; the
+    // first col_rem of them are (col_units + 1) * 16 wide, the others col_units * 16 (col_units = 16, col_rem = 0: all 256)
+    int col_count, col_units, col_rem;
 };
 
 
@@ -602,7 +605,13 @@ constexpr int NUM_BARS = 2 * P_STAGES + 2 * U_STAGES + 2 + 1 + 4 + 2 * A_STAGES;
 constexpr int LAYOUT_BYTES = U_STAGES * U_BYTES + P_STAGES * P_BYTES + VEC_BYTES + NUM_BARS * 8 + 16;
 constexpr int SMEM_BYTES = 232448;  // all the shared memory one CTA can have; the layout needs a 1024-byte aligned start
 static_assert(LAYOUT_BYTES <= SMEM_BYTES, "layout does not fit");
-constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+constexpr uint32_t IDESC_BASE = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(128 >> 4) << 24);  // + (tile width >> 3) << 17
+// First output column and width of tile column `col` (see EpilogueParams::col_count).
+__device__ __forceinline__ void column_range(const EpilogueParams& ep, int col, int& n0, int& bn) {
+    const int wider = col < ep.col_rem ? col : ep.col_rem;
+    n0 = (col * ep.col_units + wider) << 4;
+    bn = (ep.col_units + (col < ep.col_rem ? 1 : 0)) << 4;
+}
 }  // namespace wide
 
 // Copies this warp's share of a finished tile (rows part*8 .. +7, then every parts*8 further) from the local output
@@ -661,14 +670,17 @@ __device__ __forceinline__ void wide_convert_columns(const EpilogueParams& ep, c
                                                      const float* sb_mul, int n0, int N, int c_begin, int c_end,
                                                      uint32_t stage_base, int warp_row0, int lane) {
 #pragma unroll 1
-    for (int c0 = c_begin; c0 < c_end; c0 += 64) {
+    for (int cx = c_begin; cx < c_end; cx += 64) {
+        // a tile width that is no multiple of 64: the last piece starts earlier and rewrites columns of the one before
+        // it (with the same values) instead of reaching into the next tile
+        const int c0 = cx + 64 <= c_end ? cx : c_end - 64;
         if (n0 + c0 >= N) break;  // warp-uniform
         uint32_t r0[32], r1[32];
         tmem_ld32(t_row + c0, r0);
         tmem_ld32(t_row + c0 + 32, r1);
         tmem_ld_wait();
         if (FUSED && stage_base != 0) {
-            const uint32_t slab = stage_base + (uint32_t)(c0 >> 6) * 4096u;
+            const uint32_t slab = stage_base + (uint32_t)(cx >> 6) * 4096u;
             if (row_ok) {
                 const uint32_t rowaddr = slab + lane * 128;
                 uint32_t w[16];
@@ -744,8 +756,7 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int tiles_m = (M + TM - 1) / TM;
-    const int tiles_n = (N + TN - 1) / TN;
-    const int num_tiles = tiles_m * tiles_n;
+    const int num_tiles = tiles_m * ep.col_count;
     const int num_kb = (K + BK - 1) / BK;
     uint32_t pre_issued = 0;  // producer thread: copies already issued before the CTA-wide synchronisation
 
@@ -778,7 +789,8 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             if (!A8) tma_prefetch_desc(&tmap_a);
             tma_prefetch_desc(&tmap_b);
             const int m0 = ((int)blockIdx.x % tiles_m) * TM;
-            const int n0 = ((int)blockIdx.x / tiles_m) * TN;
+            int n0, bn;
+            column_range(ep, (int)blockIdx.x / tiles_m, n0, bn);
             for (; pre_issued < (uint32_t)P_STAGES && (int)pre_issued < num_kb; ++pre_issued) {
                 mbar_arrive_expect_tx(full_p + 8 * pre_issued, PB_BYTES);
                 const uint32_t dst = p_base + pre_issued * PB_BYTES;
@@ -803,7 +815,8 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             bool ok = ep.test_skip_producer == 0;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 const int m0 = (tile % tiles_m) * TM;
-                const int n0 = (tile / tiles_m) * TN;
+                int n0, bn;
+                column_range(ep, tile / tiles_m, n0, bn);
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     if (it < pre_issued) continue;  // left before the CTA synchronised
                     const uint32_t s = it % P_STAGES, ph = (it / P_STAGES) & 1u;
@@ -828,6 +841,9 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
                 const int m0 = (tile % tiles_m) * TM;
                 const int halves = (m0 + 128 < M) ? 2 : 1;  // the lower accumulator is skipped when its rows are all outside M
+                int n0, bn;
+                column_range(ep, tile / tiles_m, n0, bn);
+                const uint32_t idesc = IDESC_BASE | ((uint32_t)(bn >> 3) << 17);
                 if (!(ok = mbar_wait(tmem_empty, (local_tile & 1u) ^ 1u, 3))) break;
                 tc_fence_after();
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
@@ -845,9 +861,9 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll
                     for (int j = 0; j < BK / 32; ++j) {
                         const uint64_t db = make_smem_desc(b_addr + 32 * j);
-                        umma_i8(tmem_acc, make_smem_desc(a_addr + 32 * j), db, IDESC, (kb | j) != 0 ? 1u : 0u);
+                        umma_i8(tmem_acc, make_smem_desc(a_addr + 32 * j), db, idesc, (kb | j) != 0 ? 1u : 0u);
                         if (halves == 2)
-                            umma_i8(tmem_acc + TN, make_smem_desc(a_addr + 128 * U8_ROW + 32 * j), db, IDESC, (kb | j) != 0 ? 1u : 0u);
+                            umma_i8(tmem_acc + TN, make_smem_desc(a_addr + 128 * U8_ROW + 32 * j), db, idesc, (kb | j) != 0 ? 1u : 0u);
                     }
                     umma_commit(empty_u + 8 * s);
                     if (A8) umma_commit(empty_a + 8 * sa);
@@ -870,7 +886,8 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         bool ok = true;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
             const int m0 = (tile % tiles_m) * TM;
-            const int n0 = (tile / tiles_m) * TN;
+            int n0, bn;
+            column_range(ep, tile / tiles_m, n0, bn);
             const uint32_t slot = local_tile & 1u, slot_ph = (local_tile >> 1) & 1u;
             const int row = m0 + half * 128 + quad * 32 + lane;
             const bool row_ok = row < M;
@@ -880,7 +897,7 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 // all epilogue warps are done with the previous tile's vectors before they are overwritten
                 asm volatile("bar.sync 1, %0;" ::"n"(kEpiWarps * 32) : "memory");
                 {
-                    const bool in = n0 + et < N;
+                    const bool in = et < bn && n0 + et < N;
                     sb_add[et] = in ? ep.b_add[n0 + et] : 0;
                     sb_mul[et] = in ? bf16_to_f32(ep.b_mul[n0 + et]) : 0.f;
                 }
@@ -903,7 +920,7 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const uint32_t stage_base = staged ? u_base + (uint32_t)(half * 4 + quad) * 16384u : 0u;
             if (m0 + half * 128 < M)  // warp-uniform: otherwise this accumulator was not computed
                 wide_convert_columns<FUSED>(ep, &tmap_d, peers.m, PUSH ? ep.n_peer : 0, t_row, row, row_ok, a_add, half_a_mul,
-                                            sb_add, sb_mul, n0, N, 0, TN, stage_base, m0 + half * 128 + quad * 32, lane);
+                                            sb_add, sb_mul, n0, N, 0, bn, stage_base, m0 + half * 128 + quad * 32, lane);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tmem_empty);
@@ -917,7 +934,7 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     ok = mbar_wait(out_ready + 8 * slot, slot_ph, 18);
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;  // no named barrier follows the last tile
-                    push_tile_rows(ep, m0, n0, min(TM, M - m0), min(TN, N - n0), kPushWarps + (warp - kFirstEpi),
+                    push_tile_rows(ep, m0, n0, min(TM, M - m0), min(bn, N - n0), kPushWarps + (warp - kFirstEpi),
                                    kPushWarps + kEpiWarps, lane);
                 }
             }
@@ -952,13 +969,14 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
                 if (FUSED && ep.tma_store && tile + (int)gridDim.x >= num_tiles) break;  // the epilogue warps send the last tile
                 const int m0 = (tile % tiles_m) * TM;
-                const int n0 = (tile / tiles_m) * TN;
+                int n0, bn;
+                column_range(ep, tile / tiles_m, n0, bn);
                 const uint32_t slot = local_tile & 1u, slot_ph = (local_tile >> 1) & 1u;
                 ok = mbar_wait(out_ready + 8 * slot, slot_ph, 12);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 const int rows = min(TM, M - m0);
-                const int cols = min(TN, N - n0);
+                const int cols = min(bn, N - n0);
                 // the CTA's last tile: the epilogue warps have nothing left to do and push as well
                 const bool last = tile + (int)gridDim.x >= num_tiles;
                 push_tile_rows(ep, m0, n0, rows, cols, pw, last ? kPushWarps + kEpiWarps : kPushWarps, lane);
@@ -1226,6 +1244,28 @@ static int make_a8_map(CUtensorMap* map, const void* base, int rows, int K) {
     return r == CUDA_SUCCESS ? QB200_OK : QB200_ERR_DRIVER;
 }
 
+// Tile columns of the 256-row kernel.  All 256 wide by default.  With `balance`, where more, narrower columns fill the
+// same number of waves over the SMs (M = 2048, N = 4096 on 148 SMs: 8 x 16 = 128 tiles leave 20 SMs idle; 8 x 18 tiles
+// of 224 or 240 columns use 144 and every CTA finishes 1/16 earlier), N is cut into that many columns instead.
+static void wide_columns(EpilogueParams* ep, int M, int N, int sms, bool balance) {
+    const int tiles_m = (M + wide::TM - 1) / wide::TM;
+    ep->col_count = (N + wide::TN - 1) / wide::TN;
+    ep->col_units = wide::TN / 16;
+    ep->col_rem = 0;
+    if (const char* e = getenv("QB200_GEMM_BALANCE"))
+        if (e[0] == '0') balance = false;
+    if (!balance || sms <= 0) return;
+    const int units = (N + 15) / 16;
+    const long long waves = ((long long)tiles_m * ep->col_count + sms - 1) / sms;
+    const int most = (int)(waves * sms / tiles_m);  // the most columns that still fit these waves
+    if (most <= ep->col_count) return;
+    const int widest = (units + most - 1) / most;
+    if (widest >= wide::TN / 16 || widest < 12) return;  // nothing gained / tiles too narrow for this kernel
+    ep->col_count = most;
+    ep->col_units = units / most;
+    ep->col_rem = units % most;
+}
+
 static int launch_gemm_wide_a8(const EpilogueParams& ep_in, const void* a8, const void* b, int M, int K, int N, int sms,
                                int dev, cudaStream_t stream) {
     EpilogueParams ep = ep_in;
@@ -1244,7 +1284,8 @@ static int launch_gemm_wide_a8(const EpilogueParams& ep_in, const void* a8, cons
     CUtensorMap md;
     PeerMaps<false> peers;
     make_output_maps<false>(&md, &peers, &ep, M, N);
-    const int tiles = ((M + wide::TM - 1) / wide::TM) * ((N + wide::TN - 1) / wide::TN);
+    wide_columns(&ep, M, N, sms, true);
+    const int tiles = ((M + wide::TM - 1) / wide::TM) * ep.col_count;
     const int grid = tiles < sms ? tiles : sms;
     kernel<<<grid, wide::kThreads - 32, wide::SMEM_BYTES, stream>>>(ma, mb, md, peers, ep, M, N, K);
     return launch_status();
@@ -1266,7 +1307,8 @@ static int launch_gemm_wide_impl(const EpilogueParams& ep_in, const void* a, con
     if (st != QB200_OK) return st;
     st = make_packed_map(&mb, b, N, K, wide::TN);
     if (st != QB200_OK) return st;
-    const int tiles = ((M + wide::TM - 1) / wide::TM) * ((N + wide::TN - 1) / wide::TN);
+    wide_columns(&ep, M, N, sms, false);  // the unpack of both operands bounds this variant: narrower tiles gain nothing
+    const int tiles = ((M + wide::TM - 1) / wide::TM) * ep.col_count;
     const int grid = tiles < sms ? tiles : sms;
     const int threads = PUSH ? wide::kThreads : wide::kThreads - 32 * wide::kPushWarps;
     CUtensorMap md;

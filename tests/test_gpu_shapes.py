@@ -372,3 +372,38 @@ def test_one_call_layer_equals_the_two_op_route(m, k, n):
     torch.cuda.synchronize()
     p2, s2, r2 = quest.hadamard_quantize_int4(x2)
     assert out.equal(quest.fused_matmul_dequantize_int4_int4t_bf16(p2, wp, r2, wa, s2, ws)) and pk.equal(p2)
+
+
+# ------------------------------------------------------------------ balanced tile columns (int8-operand GEMM) ---
+@pytest.mark.parametrize("m,k,n", [
+    (2048, 256, 4096),    # 8 x 16 tiles of 256 columns -> 8 x 18 of 240 / 224
+    (2048, 128, 4000),    # the same cut with a ragged last column
+    (2048, 128, 4088),    # N no multiple of 16: the last column reaches past N and is clipped
+    (1900, 128, 14336),   # 8 x 56 -> 8 x 74 columns of 208 / 192, four waves, ragged last tile row
+    (8192, 128, 4096),    # four tiles per CTA, every one narrower
+    (1024, 256, 8192),    # 4 x 32 -> 4 x 37 columns of 224 / 208
+    (600, 128, 3000),     # too few tiles to fill the SMs with tiles of at least 192 columns: stays at 256
+])
+def test_int8_operand_gemm_with_balanced_tile_columns(m, k, n, monkeypatch):
+    """Where more, narrower tile columns fill the same number of waves over the SMs, the int8-operand GEMM cuts N into
+    columns of 192 ... 240 instead of 256 (widths multiples of 16; the last 64-column piece of a tile overlaps the one
+    before it).  Whatever the cut, the output is bit-identical to the packed route (uniform 256-column tiles), with the
+    cut switched off, and for a second launch on other data."""
+    g = torch.Generator(device=DEV).manual_seed(m + n)
+    for rnd in range(2):
+        packed = torch.randint(0, 256, (m, k // 2), dtype=torch.uint8, device=DEV, generator=g)
+        wp = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device=DEV, generator=g)
+        a_add = torch.randint(-8 * k, 8 * k, (m, 1), dtype=torch.int32, device=DEV, generator=g)
+        b_add = torch.randint(-8 * k, 8 * k, (n, 1), dtype=torch.int32, device=DEV, generator=g)
+        a_mul = (0.01 + torch.rand(m, 1, device=DEV, generator=g)).to(torch.bfloat16)
+        b_mul = (0.01 + torch.rand(n, 1, device=DEV, generator=g)).to(torch.bfloat16)
+        codes = quest.unpack_int4(packed).view(m, k // 32, 16, 2)
+        a8 = (torch.cat([codes[..., 0], codes[..., 1]], dim=-1).reshape(m, k) * 16).to(torch.int8).view(torch.uint8).contiguous()
+        ref = quest.fused_matmul_dequantize_int4_int4t_bf16(packed, wp, a_add, b_add, a_mul, b_mul)
+        out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+        quest.fused_matmul_dequantize_a8(a8, wp, a_add, b_add, a_mul, b_mul, out=out)
+        assert out.equal(ref)
+        monkeypatch.setenv("QB200_GEMM_BALANCE", "0")
+        assert quest.fused_matmul_dequantize_a8(a8, wp, a_add, b_add, a_mul, b_mul).equal(ref)
+        monkeypatch.delenv("QB200_GEMM_BALANCE")
+    assert quest.device_status() == 0

@@ -224,14 +224,20 @@ int silu_mul_hadamard_quantize_int4_cuda_bf16(void* x_int_packed_ptr, void* scal
 /*
  * The whole layer in one call: hadamard_quantize_int4_cuda_bf16 into the caller's workspaces (a_int_packed uint8
  * [M, K/2], a_scale bf16 [M], a_int_row_sum int32 [M]; all required), then the fused GEMM + epilogue into mat_d
- * bf16 [M, N] - what gemm-quest/benchmarks/utils.py:89-100 does with four launches.  Up to 16 rows the GEMM is the
- * weight-streaming kernel, whose prologue does not depend on the activations: it is launched with a programmatic
- * dependency, starts while the quantiser still runs and waits for it on the device, so the layer costs little more than
- * one launch.  Results are those of the two calls made one after the other.  No counterpart in the reference.
+ * bf16 [M, N] - what gemm-quest/benchmarks/utils.py:89-100 does with four launches.  The GEMM kernel is launched with a
+ * programmatic dependency on the quantiser: its blocks are scheduled while the quantiser's last blocks still run, set up
+ * their barriers and tensor memory, request their first weights (which do not depend on the activations) and wait on the
+ * device for the quantiser's end before they touch its outputs, so the gap between the two kernels disappears (at up to
+ * 16 rows the layer costs little more than one launch).  Results are those of the two calls made one after the other.
+ * w4a4_linear_hadamard_a8_bf16_cuda is the same for the int8-operand route (hadamard_quantize_a8_cuda_bf16 into a_int8
+ * uint8 [M, K], then fused_matmul_dequantize_a8_int4t_bf16_cuda).  No counterpart in the reference.
  */
 int w4a4_linear_hadamard_bf16_cuda(void* mat_d, const void* x, const void* w_int_packed, const void* w_add,
                                    const void* w_scale, void* a_int_packed, void* a_scale, void* a_int_row_sum, int M,
                                    int K, int N, int block, cudaStream_t stream);
+int w4a4_linear_hadamard_a8_bf16_cuda(void* mat_d, const void* x, const void* w_int_packed, const void* w_add,
+                                      const void* w_scale, void* a_int8, void* a_scale, void* a_int_row_sum, int M,
+                                      int K, int N, int block, cudaStream_t stream);
 
 /*
  * out = bf16(H_block . x) blockwise along the last dimension (out may alias x).

@@ -294,17 +294,20 @@ def w4a4_linear_hadamard(
         block: int = 128,
 ) -> torch.Tensor:
     """The layer in one library call: fused Hadamard + quantise of ``x`` into the given workspaces, then the fused GEMM
-    into ``out``.  For up to 16 rows the GEMM kernel is launched with a programmatic dependency on the quantiser (its
-    weight prefetch overlaps the quantiser); results equal the two ops called one after the other."""
+    into ``out``.  The GEMM kernel is launched with a programmatic dependency on the quantiser (its set-up and first
+    weight copies overlap the quantiser's end); results equal the two ops called one after the other.  ``a_int_packed``
+    of shape [M, K] instead of [M, K/2] selects the int8-operand route (``hadamard_quantize_a8`` +
+    ``fused_matmul_dequantize_a8``)."""
     assert x.dim() == 2 and x.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and w_int_packed.dtype == torch.uint8
     assert a_int_packed.dtype == torch.uint8 and a_scale.dtype == torch.bfloat16 and a_int_row_sum.dtype == torch.int32
     assert w_add.dtype == torch.int32 and w_scale.dtype == torch.bfloat16
     assert all(t.is_contiguous() for t in (x, w_int_packed, w_add, w_scale, out, a_int_packed, a_scale, a_int_row_sum))
     m, k = x.shape
     n = w_int_packed.size(0)
-    assert w_int_packed.size(1) * 2 == k and out.shape == (m, n) and a_int_packed.shape == (m, k // 2)
+    assert w_int_packed.size(1) * 2 == k and out.shape == (m, n) and a_int_packed.shape in ((m, k // 2), (m, k))
+    entry = "w4a4_linear_hadamard_a8_bf16_cuda" if a_int_packed.shape == (m, k) else "w4a4_linear_hadamard_bf16_cuda"
     dev = _lib.require_cuda(x, w_int_packed, w_add, w_scale, out, a_int_packed, a_scale, a_int_row_sum)
-    _call("w4a4_linear_hadamard_bf16_cuda", dev, _lib.ptr(out), _lib.ptr(x), _lib.ptr(w_int_packed), _lib.ptr(w_add),
+    _call(entry, dev, _lib.ptr(out), _lib.ptr(x), _lib.ptr(w_int_packed), _lib.ptr(w_add),
           _lib.ptr(w_scale), _lib.ptr(a_int_packed), _lib.ptr(a_scale), _lib.ptr(a_int_row_sum), m, k, n, int(block),
           _lib.stream_of(x))
     return out

@@ -26,6 +26,7 @@ SIGNATURES = {
     "fused_matmul_dequantize_int4_int4t_bf16_push_cuda": [ctypes.POINTER(ctypes.c_void_p), _I, _LL, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     "hadamard_quantize_int4_cuda_bf16": [_P, _P, _P, _P, _I, _I, _I, _P],
     "w4a4_linear_hadamard_bf16_cuda": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "w4a4_linear_hadamard_a8_bf16_cuda": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
     "hadamard_quantize_a8_cuda_bf16": [_P, _P, _P, _P, _I, _I, _I, _P],
     "rmsnorm_hadamard_quantize_int4_cuda_bf16": [_P, _P, _P, _P, _P, ctypes.c_float, _I, _I, _I, _P],
     "silu_mul_hadamard_quantize_int4_cuda_bf16": [_P, _P, _P, _P, _P, _I, _I, _I, _P],

@@ -30,6 +30,31 @@
 
 #include "tcgen05.cuh"
 
+// Set (per host thread) by the one-call layer entry points around their GEMM call: the GEMM kernel is then launched
+// with a programmatic dependency on the preceding kernel of the stream (the quantiser of its activations) instead of a
+// full one.  Its blocks are scheduled as soon as the quantiser's blocks have left the SMs, set up their barriers and
+// tensor memory and request the weights; every thread that touches what the quantiser writes (the A operand, the row
+// sums and scales) first executes griddepcontrol.wait, which returns when the quantiser's grid has completed and its
+// writes are visible.  Without the launch attribute that instruction returns at once.
+static thread_local bool tl_dependent_launch = false;
+
+__device__ __forceinline__ void wait_for_preceding_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename Kernel, typename... Args>
+static cudaError_t launch_kernel(Kernel kernel, int grid, int threads, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = tl_dependent_launch ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 namespace qb {
 
 #ifdef QB200_TRACE
@@ -272,6 +297,7 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_acc = *tmem_slot_ptr;
+    wait_for_preceding_grid();  // barriers and tensor memory are set up; everything from here on may touch the A operand
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
@@ -786,6 +812,7 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         // The first copies of the CTA's first tile leave before tensor memory is allocated and the CTA has synchronised:
         // they need nothing but the barriers initialised above (this thread is also the producer thread below).
         if (ep.test_skip_producer == 0 && (int)blockIdx.x < num_tiles) {
+            if (!A8) wait_for_preceding_grid();  // these copies include A tiles
             if (!A8) tma_prefetch_desc(&tmap_a);
             tma_prefetch_desc(&tmap_b);
             const int m0 = ((int)blockIdx.x % tiles_m) * TM;
@@ -807,6 +834,9 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_acc = *tmem_slot_ptr;
+    // The packed variants load A from the first copy on: every thread waits here.  A8: only the warps that touch the
+    // quantiser's outputs wait (A producer, epilogue), the weights are requested, copied and unpacked before.
+    if (!A8) wait_for_preceding_grid();
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
@@ -884,6 +914,7 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         float* sb_mul = reinterpret_cast<float*>(vec_ptr + TN * 4);
         uint32_t local_tile = 0;
         bool ok = true;
+        if (A8) wait_for_preceding_grid();  // the row sums and scales come from the quantiser
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
             const int m0 = (tile % tiles_m) * TM;
             int n0, bn;
@@ -943,6 +974,7 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         // ------------------------------ A operand producer (A8 only; there are no push warps then) -----------
         if (lane == 0) {
             tma_prefetch_desc(&tmap_a);
+            wait_for_preceding_grid();  // the A operand is the quantiser's output
             uint32_t it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
@@ -1087,7 +1119,10 @@ static int launch_gemm(const EpilogueParams& ep, const void* a, const void* b, i
     const int grid = items < sms ? items : sms;
     // the two push warps are the last ones of the block: without peers they are simply not launched
     const int threads = ep.n_peer > 0 ? kNumThreads : kNumThreads - 32 * kNumPushWarps;
-    kernel<<<grid, threads, C::SMEM_BYTES, stream>>>(ma, mb, ep, M, N, K);
+    if (launch_kernel(kernel, grid, threads, C::SMEM_BYTES, stream, ma, mb, ep, M, N, K) != cudaSuccess) {
+        cudaGetLastError();
+        return QB200_ERR_CUDA;
+    }
     return launch_status();
 }
 
@@ -1287,7 +1322,10 @@ static int launch_gemm_wide_a8(const EpilogueParams& ep_in, const void* a8, cons
     wide_columns(&ep, M, N, sms, true);
     const int tiles = ((M + wide::TM - 1) / wide::TM) * ep.col_count;
     const int grid = tiles < sms ? tiles : sms;
-    kernel<<<grid, wide::kThreads - 32, wide::SMEM_BYTES, stream>>>(ma, mb, md, peers, ep, M, N, K);
+    if (launch_kernel(kernel, grid, wide::kThreads - 32, wide::SMEM_BYTES, stream, ma, mb, md, peers, ep, M, N, K) != cudaSuccess) {
+        cudaGetLastError();
+        return QB200_ERR_CUDA;
+    }
     return launch_status();
 }
 
@@ -1319,7 +1357,10 @@ static int launch_gemm_wide_impl(const EpilogueParams& ep_in, const void* a, con
         memset(&md, 0, sizeof(md));
         memset(&peers, 0, sizeof(peers));
     }
-    kernel<<<grid, threads, wide::SMEM_BYTES, stream>>>(ma, mb, md, peers, ep, M, N, K);
+    if (launch_kernel(kernel, grid, threads, wide::SMEM_BYTES, stream, ma, mb, md, peers, ep, M, N, K) != cudaSuccess) {
+        cudaGetLastError();
+        return QB200_ERR_CUDA;
+    }
     return launch_status();
 }
 
@@ -1591,12 +1632,26 @@ extern "C" int w4a4_linear_hadamard_bf16_cuda(void* mat_d, const void* x, const 
     if (!a_int_row_sum) return QB200_ERR_INVALID_ARGUMENT;
     const int st = hadamard_quantize_int4_cuda_bf16(a_int_packed, a_scale, a_int_row_sum, x, K, M, block, stream);
     if (st != QB200_OK) return st;
-    // Up to 16 rows the GEMM is the weight-streaming dp4a kernel, whose prologue (the first weights of every warp) does
-    // not depend on the activations: it is launched with a programmatic dependency, starts while the quantiser still
-    // runs and waits for it on the device.  Larger shapes take the ordinary, fully ordered launch.
+    // The GEMM kernel is launched with a programmatic dependency: it starts while the quantiser's last blocks still
+    // run, sets itself up, requests its first weights and waits for the quantiser on the device (see tl_dependent_launch).
     tl_dependent_launch = true;
     const int st2 = fused_matmul_dequantize_int4_int4t_bf16_cuda(mat_d, a_int_packed, w_int_packed, a_int_row_sum, w_add,
                                                                  a_scale, w_scale, M, K, N, stream);
+    tl_dependent_launch = false;
+    return st2;
+}
+
+extern "C" int hadamard_quantize_a8_cuda_bf16(void*, void*, void*, const void*, int, int, int, cudaStream_t);
+
+extern "C" int w4a4_linear_hadamard_a8_bf16_cuda(void* mat_d, const void* x, const void* w_int_packed, const void* w_add,
+                                                 const void* w_scale, void* a_int8, void* a_scale, void* a_int_row_sum,
+                                                 int M, int K, int N, int block, cudaStream_t stream) {
+    if (!a_int_row_sum) return QB200_ERR_INVALID_ARGUMENT;
+    const int st = hadamard_quantize_a8_cuda_bf16(a_int8, a_scale, a_int_row_sum, x, K, M, block, stream);
+    if (st != QB200_OK) return st;
+    tl_dependent_launch = true;
+    const int st2 = fused_matmul_dequantize_a8_int4t_bf16_cuda(mat_d, a_int8, w_int_packed, a_int_row_sum, w_add, a_scale,
+                                                               w_scale, M, K, N, stream);
     tl_dependent_launch = false;
     return st2;
 }

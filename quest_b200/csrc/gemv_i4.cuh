@@ -13,10 +13,6 @@
 // Replaces, for these shapes, gemm-quest/quest/matmul_kernel.cu:8-63 and fused_matmul_dequantize_kernel.cu:4-57.
 #pragma once
 
-// Set (per host thread) by the fused layer entry point around its GEMM call: the small-M kernel is then launched with
-// a programmatic dependency on the preceding kernel of the stream instead of a full one.
-static thread_local bool tl_dependent_launch = false;
-
 namespace gemv {
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
@@ -55,7 +51,7 @@ gemv_i4_kernel(const uint8_t* __restrict__ A, const uint8_t* __restrict__ B, con
     load_weights(wcur, group * C, group < groups ? lane : chunks);
     // Launched with a programmatic dependency on the kernel that quantises the activations (fused layer call), this
     // grid starts while that kernel still runs: everything up to here touches only the weights.  Now wait for it.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    wait_for_preceding_grid();
     for (int i = threadIdx.x; i < MR * chunks; i += gemv::kThreads) {
         const int r = i / chunks, ch = i - r * chunks;
         gemv_sA[i] = r < M ? *reinterpret_cast<const uint4*>(A + (size_t)r * row_bytes + (size_t)ch * 16) : make_uint4(0, 0, 0, 0);

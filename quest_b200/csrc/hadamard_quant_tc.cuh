@@ -78,6 +78,9 @@ hadamard_quant_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const RowPa
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    // A GEMM launched behind this kernel with a programmatic dependency may be scheduled as soon as every block of this
+    // grid has got here (it waits on the device for this grid's end before it touches anything written here).
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 #ifdef QB200_TRACE
     if (threadIdx.x == 0) {
         const unsigned long long t = hq_gtime();

@@ -16,7 +16,6 @@ import quest_b200 as quest
 from .workspace import default_cache
 
 HADAMARD_BLOCK = 128  # the reference hard-codes block 128 (utils.py:17, 39, 90)
-SMALL_M_ONE_CALL = 16  # up to this many rows linear_forward makes ONE library call for the whole layer
 
 
 def preprocess_weight(
@@ -79,6 +78,11 @@ def fused_matmul_dequantize_int4_bf16(
     return mat_d
 
 
+def _one_call_ok(*tensors: torch.Tensor) -> bool:
+    """The one-call layer entry points take dense row-major buffers only."""
+    return all(t.is_contiguous() for t in tensors)
+
+
 def linear_forward(
         activation: torch.Tensor,
         w_int_packed: torch.Tensor,
@@ -103,7 +107,10 @@ def linear_forward(
 
     With ``use_hadamard`` and a shape for which the library prefers it, the quantiser writes the GEMM's int8 operand
     directly (``_a_int8`` [M, K] uint8 is its workspace) instead of packed int4: same codes, same result, no unpack
-    of A inside the GEMM.  A caller that passes ``_a_int_packed`` but no ``_a_int8`` keeps the packed route."""
+    of A inside the GEMM.  A caller that passes ``_a_int_packed`` but no ``_a_int8`` keeps the packed route.
+
+    With ``use_hadamard`` (and dense buffers) the layer is ONE library call: the quantiser, then the GEMM kernel launched
+    with a programmatic dependency on it, so that the GEMM's set-up and first weight copies overlap the quantiser's end."""
     if w_meta_e is not None:
         raise NotImplementedError("quest_b200 implements the dense W4A4 path only")
     M, K, N = activation.size(0), activation.size(1), w_int_packed.size(0)
@@ -115,13 +122,16 @@ def linear_forward(
     if (use_hadamard and not debug_mode and (_a_int8 is not None or _a_int_packed is None) and K % block == 0
             and quest.prefers_a8(M, K, N)):
         a_int8 = torch.empty(M, K, dtype=torch.uint8, device=device) if _a_int8 is None else _a_int8
+        if _one_call_ok(activation, out, a_int8, a_scale, a_int_row_sum, w_int_packed, w_add, w_scale):
+            return quest.w4a4_linear_hadamard(activation, w_int_packed, w_add, w_scale, out, a_int8, a_scale, a_int_row_sum,
+                                              block=block)
         quest.hadamard_quantize_a8(activation, block=block, x_a8=a_int8, scale=a_scale, x_int_row_sum=a_int_row_sum)
         quest.fused_matmul_dequantize_a8(mat_a8=a_int8, mat_b=w_int_packed, vec_a_add=a_int_row_sum, vec_b_add=w_add,
                                          vec_a_mul=a_scale, vec_b_mul=w_scale, out=out)
         return out
     a_int_packed = torch.empty(M, K // 2, dtype=torch.uint8, device=device) if _a_int_packed is None else _a_int_packed
-    if use_hadamard and not debug_mode and M <= SMALL_M_ONE_CALL and out.is_contiguous():
-        # few rows: one library call; the weight-streaming GEMM starts behind the quantiser with a dependent launch
+    if use_hadamard and not debug_mode and _one_call_ok(activation, out, a_int_packed, a_scale, a_int_row_sum, w_int_packed, w_add, w_scale):
+        # one library call: the GEMM kernel starts behind the quantiser with a dependent launch
         return quest.w4a4_linear_hadamard(activation, w_int_packed, w_add, w_scale, out, a_int_packed, a_scale, a_int_row_sum,
                                           block=block)
     if use_hadamard:

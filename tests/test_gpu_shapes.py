@@ -338,12 +338,12 @@ def test_prefill_fused_blocks_track_the_unfused_model():
 
 
 # ------------------------------------------------------------------ the layer in one call (few rows) ---
-@pytest.mark.parametrize("m", [1, 3, 16])
+@pytest.mark.parametrize("m", [1, 3, 16, 200, 2048])
 @pytest.mark.parametrize("k,n", [(4096, 4096), (5632, 2048), (8192, 1280)])
 def test_one_call_layer_equals_the_two_op_route(m, k, n):
-    """Up to 16 rows linear_forward makes one library call whose GEMM kernel is launched with a programmatic dependency
-    on the quantiser: the workspaces and the output must hold exactly what the two ops called one after the other
-    give, call after call, and also when the call is replayed from a CUDA graph."""
+    """linear_forward makes one library call whose GEMM kernel (dp4a, split-K, 128-row or 256-row tiles, by shape) is
+    launched with a programmatic dependency on the quantiser: the workspaces and the output must hold exactly what the
+    two ops called one after the other give, call after call, and also when the call is replayed from a CUDA graph."""
     x = make_activations("student", m, k, seed=m + k).to(DEV)
     w = (0.02 * torch.randn(n, k, generator=torch.Generator().manual_seed(n))).to(torch.bfloat16).to(DEV)
     wp, ws, wa, _ = quest.preprocess_weight(w, use_hadamard=True)
@@ -406,4 +406,46 @@ def test_int8_operand_gemm_with_balanced_tile_columns(m, k, n, monkeypatch):
         monkeypatch.setenv("QB200_GEMM_BALANCE", "0")
         assert quest.fused_matmul_dequantize_a8(a8, wp, a_add, b_add, a_mul, b_mul).equal(ref)
         monkeypatch.delenv("QB200_GEMM_BALANCE")
+    assert quest.device_status() == 0
+
+
+@pytest.mark.parametrize("m,k,n", [(2048, 4096, 4096), (1024, 4096, 14336), (4096, 8192, 1024)])
+def test_one_call_layer_on_the_int8_operand_route(m, k, n):
+    """The same for the int8-operand route: the 256-row GEMM kernel starts behind the tcgen05 quantiser, copies and
+    unpacks its first weights and waits on the device before its first A copy and before reading the row sums."""
+    if not quest.prefers_a8(m, k, n):
+        pytest.skip("the library does not choose the int8 operand for this shape")
+    w = (0.02 * torch.randn(n, k, generator=torch.Generator().manual_seed(n))).to(torch.bfloat16).to(DEV)
+    wp, ws, wa, _ = quest.preprocess_weight(w, use_hadamard=True)
+    a8 = torch.zeros(m, k, dtype=torch.uint8, device=DEV)
+    sc = torch.zeros(m, 1, dtype=torch.bfloat16, device=DEV)
+    rs = torch.zeros(m, 1, dtype=torch.int32, device=DEV)
+    out = torch.zeros(m, n, dtype=torch.bfloat16, device=DEV)
+    x = make_activations("student", m, k, seed=m + k).to(DEV)
+
+    def two_ops(xx):
+        q, s_, r_ = quest.hadamard_quantize_a8(xx, 128)
+        return q, s_, r_, quest.fused_matmul_dequantize_a8(q, wp, r_, wa, s_, ws)
+
+    q_ref, s_ref, r_ref, y_ref = two_ops(x)
+    for _ in range(3):
+        out.zero_()
+        y = quest.linear_forward(x, wp, ws, wa, out=out, _a_scale=sc, _a_int8=a8, _a_int_row_sum=rs, use_hadamard=True)
+        assert y is out and out.equal(y_ref) and a8.equal(q_ref) and sc.equal(s_ref) and rs.equal(r_ref)
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        quest.linear_forward(x, wp, ws, wa, out=out, _a_scale=sc, _a_int8=a8, _a_int_row_sum=rs, use_hadamard=True)
+    torch.cuda.current_stream().wait_stream(s)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(3):  # back to back: a quantiser overwrites the operand the GEMM before it has read
+            quest.linear_forward(x, wp, ws, wa, out=out, _a_scale=sc, _a_int8=a8, _a_int_row_sum=rs, use_hadamard=True)
+    for seed in (7, 8):
+        x.copy_(make_activations("randn", m, k, seed=seed).to(DEV))
+        out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        q2, s2, r2, y2 = two_ops(x)
+        assert out.equal(y2) and a8.equal(q2) and sc.equal(s2) and rs.equal(r2)
     assert quest.device_status() == 0

@@ -27,6 +27,34 @@ inline int launch_status() {
     return cuda_status(e);
 }
 
+// Programmatic dependent launches.  A kernel launched with `dependent` may be scheduled before the kernel that
+// precedes it in the stream has completed (as soon as all of that kernel's blocks have executed
+// griddepcontrol.launch_dependents or left); it must execute griddepcontrol.wait - which returns when the preceding grid
+// has completed and its writes are visible - before its first access to global memory that the preceding kernel may
+// write or still read.  Without the attribute both instructions do nothing.
+__device__ __forceinline__ void wait_for_preceding_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void let_dependents_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename Kernel, typename... Args>
+inline cudaError_t launch_kernel_dep(bool dependent, Kernel kernel, long long grid, int threads, size_t smem,
+                                     cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = dependent ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
+// Set (per host thread) by the one-call layer entry points around their quantiser call: the tcgen05 and mma.sync
+// quantiser kernels (the ones that wait on the device) are then launched with a programmatic dependency.
+extern thread_local bool qb_tl_dependent_quantiser;
+
 // Reads and clears the device status word of the row-kernel translation unit (see tcgen05.cuh).
 int hq_tc_fetch_and_clear_device_status(int* out);
 

@@ -38,21 +38,9 @@
 // writes are visible.  Without the launch attribute that instruction returns at once.
 static thread_local bool tl_dependent_launch = false;
 
-__device__ __forceinline__ void wait_for_preceding_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-
 template <typename Kernel, typename... Args>
 static cudaError_t launch_kernel(Kernel kernel, int grid, int threads, size_t smem, cudaStream_t stream, Args... args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3((unsigned)threads);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = tl_dependent_launch ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kernel, args...);
+    return qb::launch_kernel_dep(tl_dependent_launch, kernel, grid, threads, smem, stream, args...);
 }
 
 namespace qb {
@@ -297,6 +285,10 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_acc = *tmem_slot_ptr;
+    // Tensor memory is allocated: a kernel launched behind this one with a programmatic dependency (the next layer's
+    // quantiser, which waits on the device) may be scheduled from now on.  Not earlier: a dependent block that shared
+    // the SM and took the tensor memory first would wait for this grid while this block waits for the allocation.
+    let_dependents_launch();
     wait_for_preceding_grid();  // barriers and tensor memory are set up; everything from here on may touch the A operand
 
     if (warp == 0) {
@@ -834,6 +826,7 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_acc = *tmem_slot_ptr;
+    let_dependents_launch();  // only now that tensor memory is allocated (see gemm_i4_kernel)
     // The packed variants load A from the first copy on: every thread waits here.  A8: only the warps that touch the
     // quantiser's outputs wait (A producer, epilogue), the weights are requested, copied and unpacked before.
     if (!A8) wait_for_preceding_grid();
@@ -1630,7 +1623,12 @@ extern "C" int w4a4_linear_hadamard_bf16_cuda(void* mat_d, const void* x, const 
                                               const void* w_scale, void* a_int_packed, void* a_scale, void* a_int_row_sum,
                                               int M, int K, int N, int block, cudaStream_t stream) {
     if (!a_int_row_sum) return QB200_ERR_INVALID_ARGUMENT;
+    // The quantiser, too, is launched with a programmatic dependency (on whatever kernel precedes the layer in the
+    // stream): it executes griddepcontrol.wait before its first access to global memory, so this is safe behind any
+    // kernel, and behind one of this library's GEMMs (layers back to back) its blocks are scheduled as the GEMM's leave.
+    qb_tl_dependent_quantiser = true;
     const int st = hadamard_quantize_int4_cuda_bf16(a_int_packed, a_scale, a_int_row_sum, x, K, M, block, stream);
+    qb_tl_dependent_quantiser = false;
     if (st != QB200_OK) return st;
     // The GEMM kernel is launched with a programmatic dependency: it starts while the quantiser's last blocks still
     // run, sets itself up, requests its first weights and waits for the quantiser on the device (see tl_dependent_launch).
@@ -1647,7 +1645,9 @@ extern "C" int w4a4_linear_hadamard_a8_bf16_cuda(void* mat_d, const void* x, con
                                                  const void* w_scale, void* a_int8, void* a_scale, void* a_int_row_sum,
                                                  int M, int K, int N, int block, cudaStream_t stream) {
     if (!a_int_row_sum) return QB200_ERR_INVALID_ARGUMENT;
+    qb_tl_dependent_quantiser = true;  // see w4a4_linear_hadamard_bf16_cuda
     const int st = hadamard_quantize_a8_cuda_bf16(a_int8, a_scale, a_int_row_sum, x, K, M, block, stream);
+    qb_tl_dependent_quantiser = false;
     if (st != QB200_OK) return st;
     tl_dependent_launch = true;
     const int st2 = fused_matmul_dequantize_a8_int4t_bf16_cuda(mat_d, a_int8, w_int_packed, a_int_row_sum, w_add, a_scale,

@@ -30,6 +30,7 @@ template <int MR, int C, bool FUSED>
 __global__ void __launch_bounds__(gemv::kThreads)
 gemv_i4_kernel(const uint8_t* __restrict__ A, const uint8_t* __restrict__ B, const EpilogueParams ep, const int M,
                const int N, const int K) {
+    let_dependents_launch();
     extern __shared__ uint4 gemv_sA[];  // [MR][K / 32] chunks of 16 packed bytes
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int chunks = K >> 5;          // 32 codes = 16 bytes per chunk
@@ -151,17 +152,7 @@ static int launch_gemv(const EpilogueParams& ep, const void* a, const void* b, i
     int grid = (groups + gemv::kWarps - 1) / gemv::kWarps;
     const int per_sm = smem > 100 * 1024 ? 1 : (smem > 48 * 1024 ? 2 : 4);
     if (grid > sms * per_sm) grid = sms * per_sm;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(gemv::kThreads);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = tl_dependent_launch ? 1 : 0;  // the fused layer call: start behind the quantiser without waiting for its end
-    if (cudaLaunchKernelEx(&cfg, kernel, static_cast<const uint8_t*>(a), static_cast<const uint8_t*>(b), ep, M, N, K) != cudaSuccess) {
+    if (launch_kernel(kernel, grid, gemv::kThreads, smem, stream, static_cast<const uint8_t*>(a), static_cast<const uint8_t*>(b), ep, M, N, K) != cudaSuccess) {
         cudaGetLastError();
         return QB200_ERR_CUDA;
     }

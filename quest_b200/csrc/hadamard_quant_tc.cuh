@@ -78,9 +78,6 @@ hadamard_quant_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const RowPa
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    // A GEMM launched behind this kernel with a programmatic dependency may be scheduled as soon as every block of this
-    // grid has got here (it waits on the device for this grid's end before it touches anything written here).
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 #ifdef QB200_TRACE
     if (threadIdx.x == 0) {
         const unsigned long long t = hq_gtime();
@@ -110,6 +107,11 @@ hadamard_quant_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const RowPa
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_acc = *tmem_slot_ptr;
+    // A GEMM launched behind this kernel with a programmatic dependency may be scheduled as soon as every block of this
+    // grid has got here (it waits on the device for this grid's end before it touches anything written here).  Only now
+    // that tensor memory is allocated: a dependent block that took it first on a shared SM would wait for this grid
+    // while this block waits for the allocation.
+    let_dependents_launch();
     const int rows_per_tile = P == 1 ? T * nb : nb / P;
     const int unit_rows = P == 1 ? T * nb : nb;  // rows of X2 per unit
 
@@ -138,12 +140,14 @@ hadamard_quant_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const RowPa
         }
         fence_proxy_async_smem();
         asm volatile("bar.sync 1, %0;" ::"n"(kThreads - 32) : "memory");
+        wait_for_preceding_grid();  // the outputs may still be read by the kernel before this one (the producer thread waits too)
     }
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             tma_prefetch_desc(&tmap_x);
+            wait_for_preceding_grid();  // launched with a programmatic dependency: the input may still be being written
             uint32_t it = 0;
             bool ok = true;
             for (;; ++it) {  // tile `it` of this CTA: part it % P of unit blockIdx.x + (it / P) * gridDim.x
@@ -454,7 +458,10 @@ static int launch_hq_tc_impl(const RowParams& p, cudaStream_t stream) {
     const int st = make_block_map(&map, p.x, (long long)p.M * nb);
     if (st != QB200_OK) return st;
     const int grid = num_units < sms ? num_units : sms;
-    kernel<<<grid, tc::kThreads, tc::SMEM_BYTES, stream>>>(map, p, nb, T, P, num_units);
+    if (launch_kernel_dep(qb_tl_dependent_quantiser, kernel, grid, tc::kThreads, tc::SMEM_BYTES, stream, map, p, nb, T, P, num_units) != cudaSuccess) {
+        cudaGetLastError();
+        return QB200_ERR_CUDA;
+    }
     return launch_status();
 }
 

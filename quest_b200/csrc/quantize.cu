@@ -16,6 +16,8 @@
 
 namespace qb {
 
+thread_local bool qb_tl_dependent_quantiser = false;
+
 struct RowParams {
     const __nv_bfloat16* x;        // [M,K] input
     __nv_bfloat16* x_out;          // optional [M,K] output (transformed or dequantised values)
@@ -368,7 +370,8 @@ hadamard_quant_mma_kernel(const RowParams p, const int W, const int G, const int
 #endif
     // A kernel launched behind this one with a programmatic dependency (the small-M GEMM of the fused layer call) may
     // start its own prologue now; it waits for this grid's results itself.  Without such a dependent this does nothing.
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    let_dependents_launch();
+    wait_for_preceding_grid();  // launched with a programmatic dependency itself (one-call layer): nothing in global memory is touched before
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const int grp = warp / W;      // row group of this warp
@@ -743,7 +746,10 @@ static int launch_hq_mma(const RowParams& p, cudaStream_t stream) {
             grid = (long long)sms * occupancy(1);
         }
         if (grid > batches) grid = batches;
-        kernel<<<(unsigned)grid, 32 * warps, (size_t)warps * per * nbuf * kStepIn, stream>>>(p, W, G, nbuf);
+        if (launch_kernel_dep(qb_tl_dependent_quantiser, kernel, grid, 32 * warps, (size_t)warps * per * nbuf * kStepIn, stream, p, W, G, nbuf) != cudaSuccess) {
+            cudaGetLastError();
+            return QB200_ERR_CUDA;
+        }
         return launch_status();
     };
     if (per == 1) return launch(hadamard_quant_mma_kernel<HB, 1, PRO>, 0);

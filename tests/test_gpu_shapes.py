@@ -437,15 +437,22 @@ def test_one_call_layer_on_the_int8_operand_route(m, k, n):
     with torch.cuda.stream(s):
         quest.linear_forward(x, wp, ws, wa, out=out, _a_scale=sc, _a_int8=a8, _a_int_row_sum=rs, use_hadamard=True)
     torch.cuda.current_stream().wait_stream(s)
+    # Layers back to back on shared workspaces: the next layer's quantiser is launched with a programmatic dependency on
+    # this layer's GEMM, so it must not overwrite the operand, scales or row sums before that GEMM has read them.
+    xb = make_activations("student", m, k, seed=5).to(DEV)
+    outs = [torch.zeros(m, n, dtype=torch.bfloat16, device=DEV) for _ in range(4)]
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph):
-        for _ in range(3):  # back to back: a quantiser overwrites the operand the GEMM before it has read
-            quest.linear_forward(x, wp, ws, wa, out=out, _a_scale=sc, _a_int8=a8, _a_int_row_sum=rs, use_hadamard=True)
+        for i, o in enumerate(outs):
+            quest.linear_forward(x if i % 2 == 0 else xb, wp, ws, wa, out=o, _a_scale=sc, _a_int8=a8, _a_int_row_sum=rs, use_hadamard=True)
     for seed in (7, 8):
         x.copy_(make_activations("randn", m, k, seed=seed).to(DEV))
-        out.zero_()
+        xb.copy_(make_activations("student", m, k, seed=seed + 10).to(DEV))
+        for o in outs:
+            o.zero_()
         graph.replay()
         torch.cuda.synchronize()
-        q2, s2, r2, y2 = two_ops(x)
-        assert out.equal(y2) and a8.equal(q2) and sc.equal(s2) and rs.equal(r2)
+        ya, yb = two_ops(x)[3], two_ops(xb)
+        assert outs[0].equal(ya) and outs[2].equal(ya) and outs[1].equal(yb[3]) and outs[3].equal(yb[3])
+        assert a8.equal(yb[0]) and sc.equal(yb[1]) and rs.equal(yb[2])
     assert quest.device_status() == 0

@@ -992,23 +992,27 @@ def run_sweep(args):
             x = torch.randn(m, 4096, generator=g, device=dev).to(torch.bfloat16)
             sc = torch.empty(m, 1, dtype=torch.bfloat16, device=dev)
             rs = torch.empty(m, 1, dtype=torch.int32, device=dev)
-            gemm_bytes = m * 2048 + n * 2048 + 2.0 * m * n + 6.0 * (m + n)
+            a8 = quest.prefers_a8(m, 4096, n)  # the route linear_forward takes for this shape
+            code_bytes = m * (4096 if a8 else 2048)
+            gemm_bytes = code_bytes + n * 2048 + 2.0 * m * n + 6.0 * (m + n)
             ns = sets_for(gemm_bytes)
-            sets = [(x.clone(), torch.empty(m, 2048, dtype=torch.uint8, device=dev), wp.clone(),
+            sets = [(x.clone(), torch.empty(m, 4096 if a8 else 2048, dtype=torch.uint8, device=dev), wp.clone(),
                      torch.empty(m, n, dtype=torch.bfloat16, device=dev)) for _ in range(ns)]
+            f1 = quest.hadamard_quantize_a8 if a8 else quest.hadamard_quantize_int4
+            mm = quest.fused_matmul_dequantize_a8 if a8 else quest.fused_matmul_dequantize_int4_int4t_bf16
             for s in sets:
-                quest.hadamard_quantize_int4(s[0], 128, s[1], sc, rs)
+                f1(s[0], 128, s[1], sc, rs)
             reps = max(1, 40 // ns)
-            t_q = rotating_sets_time(lambda i: quest.hadamard_quantize_int4(sets[i][0], 128, sets[i][1], sc, rs), ns, reps, dev)
-            t_g = rotating_sets_time(lambda i: quest.fused_matmul_dequantize_int4_int4t_bf16(sets[i][1], sets[i][2], rs, wa, sc, ws, sets[i][3]),
-                                     ns, reps, dev)
+            t_q = rotating_sets_time(lambda i: f1(sets[i][0], 128, sets[i][1], sc, rs), ns, reps, dev)
+            t_g = rotating_sets_time(lambda i: mm(sets[i][1], sets[i][2], rs, wa, sc, ws, sets[i][3]), ns, reps, dev)
 
             def both(i):  # the layer as linear_forward runs it (one library call, the GEMM launched behind the quantiser)
-                quest.linear_forward(sets[i][0], sets[i][2], ws, wa, out=sets[i][3], _a_scale=sc, _a_int_packed=sets[i][1],
-                                     _a_int_row_sum=rs, use_hadamard=True)
+                ws_kw = {"_a_int8": sets[i][1]} if a8 else {"_a_int_packed": sets[i][1]}
+                quest.linear_forward(sets[i][0], sets[i][2], ws, wa, out=sets[i][3], _a_scale=sc, _a_int_row_sum=rs,
+                                     use_hadamard=True, **ws_kw)
             t_l = rotating_sets_time(both, ns, reps, dev)
             ops = 2.0 * m * n * 4096
-            linear.append({"M": m, "N": n, "K": 4096, "quantize_us": t_q * 1e6, "gemm_us": t_g * 1e6, "layer_us": t_l * 1e6,
+            linear.append({"M": m, "N": n, "K": 4096, "route": "int8 operand" if a8 else "packed int4", "quantize_us": t_q * 1e6, "gemm_us": t_g * 1e6, "layer_us": t_l * 1e6,
                            "gemm_tops": ops / t_g / 1e12, "gemm_frac_int8_peak": ops / t_g / 1e12 / (2 * peaks["bf16_tflops"]),
                            "gemm_gbs": gemm_bytes / t_g / 1e9, "gemm_frac_hbm": gemm_bytes / t_g / 1e9 / peaks["hbm_gbs"],
                            "layer_tops": ops / t_l / 1e12, "sets": ns})

@@ -240,6 +240,16 @@ int w4a4_linear_hadamard_a8_bf16_cuda(void* mat_d, const void* x, const void* w_
                                       int K, int N, int block, cudaStream_t stream);
 
 /*
+ * State of the calling host thread; returns the previous value.  While on, every GEMM kernel this thread launches
+ * through the fused entry points (fused_matmul_dequantize_*) carries a programmatic dependency on the kernel before it
+ * in its stream, exactly as inside w4a4_linear_hadamard_bf16_cuda: the GEMM reads its weights (mat_b) before it waits on
+ * the device for that kernel, everything else after.  The caller promises that the preceding kernel does not write
+ * mat_b.  The package's column-sharded layer turns it on around the GEMM that follows its quantiser.  No counterpart in
+ * the reference.
+ */
+int quest_b200_set_dependent_gemm_launch(int on);
+
+/*
  * out = bf16(H_block . x) blockwise along the last dimension (out may alias x).
  * weight_side == 0: entries +-bf16(block^-0.5), the activation-side matrix of
  * gemm-quest/benchmarks/utils.py:17,89-90.  weight_side != 0: entries +-fp32(block^-0.5), the

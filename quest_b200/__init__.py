@@ -313,6 +313,20 @@ def w4a4_linear_hadamard(
     return out
 
 
+class dependent_gemm_launch:
+    """Context manager: fused GEMMs launched by this thread inside it start behind the preceding kernel of their stream
+    with a programmatic dependency (they read their weights first and wait on the device before anything else), as the
+    one-call layer does.  Only around a GEMM whose preceding kernel does not write its weights."""
+
+    def __enter__(self):
+        self._prev = _lib.load().quest_b200_set_dependent_gemm_launch(1)
+        return self
+
+    def __exit__(self, *exc):
+        _lib.load().quest_b200_set_dependent_gemm_launch(self._prev)
+        return False
+
+
 def prefers_a8(m: int, k: int, n: int) -> bool:
     """Whether the int8-operand route (``hadamard_quantize_a8`` + ``fused_matmul_dequantize_a8``) is the faster one
     for a layer of this shape."""

@@ -1656,6 +1656,12 @@ extern "C" int w4a4_linear_hadamard_a8_bf16_cuda(void* mat_d, const void* x, con
     return st2;
 }
 
+extern "C" int quest_b200_set_dependent_gemm_launch(int on) {
+    const int prev = tl_dependent_launch ? 1 : 0;
+    tl_dependent_launch = on != 0;
+    return prev;
+}
+
 extern "C" int quest_b200_test_bounded_wait_cuda(void* mat_d, const void* mat_a, const void* mat_b, const void* vec_a_add,
                                                  const void* vec_b_add, const void* vec_a_mul, const void* vec_b_mul, int M,
                                                  int K, int N, long long wait_limit_cycles, cudaStream_t stream) {

@@ -78,8 +78,9 @@ class ShardedLinear4bit:
         self.quantize_activations(x, ws)
         if self._stage is not None:
             self._stage("quantised")
-        quest.fused_matmul_dequantize_int4_int4t_bf16_into(ws["a_int_packed"], self.w_int_packed, ws["a_int_row_sum"],
-                                                           self.w_add, ws["a_scale"], self.w_scale, out_cols)
+        with quest.dependent_gemm_launch():
+            quest.fused_matmul_dequantize_int4_int4t_bf16_into(ws["a_int_packed"], self.w_int_packed, ws["a_int_row_sum"],
+                                                               self.w_add, ws["a_scale"], self.w_scale, out_cols)
 
     def quantize_activations(self, x: torch.Tensor, ws: dict) -> None:
         if self.use_hadamard:
@@ -156,9 +157,10 @@ class ShardedLinear4bit:
             else:
                 off = self.n0 * t.element_size()
                 order = [self.rank] + [(self.rank + i) % self.world for i in range(1, self.world)]
-                quest.fused_matmul_dequantize_int4_int4t_bf16_push(
-                    ws["a_int_packed"], self.w_int_packed, ws["a_int_row_sum"], self.w_add, ws["a_scale"], self.w_scale,
-                    [ptrs[r] + off for r in order], self.n_total)
+                with quest.dependent_gemm_launch():  # the GEMM sets itself up and fetches weights behind the quantiser
+                    quest.fused_matmul_dequantize_int4_int4t_bf16_push(
+                        ws["a_int_packed"], self.w_int_packed, ws["a_int_row_sum"], self.w_add, ws["a_scale"], self.w_scale,
+                        [ptrs[r] + off for r in order], self.n_total)
             stage("computed")
             hdl.barrier(channel=0)  # every rank's tiles have landed everywhere
             return t

@@ -51,8 +51,8 @@ inline cudaError_t launch_kernel_dep(bool dependent, Kernel kernel, long long gr
     return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
-// Set (per host thread) by the one-call layer entry points around their quantiser call: the tcgen05 and mma.sync
-// quantiser kernels (the ones that wait on the device) are then launched with a programmatic dependency.
+// Set (per host thread) by the one-call layer entry points around their quantiser call: the tcgen05 quantiser kernel
+// (which waits on the device) is then launched with a programmatic dependency.
 extern thread_local bool qb_tl_dependent_quantiser;
 
 // Reads and clears the device status word of the row-kernel translation unit (see tcgen05.cuh).

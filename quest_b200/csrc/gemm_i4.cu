@@ -1619,6 +1619,12 @@ extern "C" int fused_matmul_dequantize_int4_int4t_bf16_cuda(void* mat_d, const v
 
 extern "C" int hadamard_quantize_int4_cuda_bf16(void*, void*, void*, const void*, int, int, int, cudaStream_t);
 
+// QB200_DEPENDENT_LAUNCH=0 in the environment: the one-call layer launches its two kernels in plain stream order.
+static bool dependent_launches_enabled() {
+    const char* e = getenv("QB200_DEPENDENT_LAUNCH");
+    return e == nullptr || e[0] != '0';
+}
+
 extern "C" int w4a4_linear_hadamard_bf16_cuda(void* mat_d, const void* x, const void* w_int_packed, const void* w_add,
                                               const void* w_scale, void* a_int_packed, void* a_scale, void* a_int_row_sum,
                                               int M, int K, int N, int block, cudaStream_t stream) {
@@ -1626,13 +1632,14 @@ extern "C" int w4a4_linear_hadamard_bf16_cuda(void* mat_d, const void* x, const 
     // The quantiser, too, is launched with a programmatic dependency (on whatever kernel precedes the layer in the
     // stream): it executes griddepcontrol.wait before its first access to global memory, so this is safe behind any
     // kernel, and behind one of this library's GEMMs (layers back to back) its blocks are scheduled as the GEMM's leave.
-    qb_tl_dependent_quantiser = true;
+    const bool dep = dependent_launches_enabled();
+    qb_tl_dependent_quantiser = dep;
     const int st = hadamard_quantize_int4_cuda_bf16(a_int_packed, a_scale, a_int_row_sum, x, K, M, block, stream);
     qb_tl_dependent_quantiser = false;
     if (st != QB200_OK) return st;
     // The GEMM kernel is launched with a programmatic dependency: it starts while the quantiser's last blocks still
     // run, sets itself up, requests its first weights and waits for the quantiser on the device (see tl_dependent_launch).
-    tl_dependent_launch = true;
+    tl_dependent_launch = dep;
     const int st2 = fused_matmul_dequantize_int4_int4t_bf16_cuda(mat_d, a_int_packed, w_int_packed, a_int_row_sum, w_add,
                                                                  a_scale, w_scale, M, K, N, stream);
     tl_dependent_launch = false;
@@ -1645,11 +1652,12 @@ extern "C" int w4a4_linear_hadamard_a8_bf16_cuda(void* mat_d, const void* x, con
                                                  const void* w_scale, void* a_int8, void* a_scale, void* a_int_row_sum,
                                                  int M, int K, int N, int block, cudaStream_t stream) {
     if (!a_int_row_sum) return QB200_ERR_INVALID_ARGUMENT;
-    qb_tl_dependent_quantiser = true;  // see w4a4_linear_hadamard_bf16_cuda
+    const bool dep = dependent_launches_enabled();
+    qb_tl_dependent_quantiser = dep;  // see w4a4_linear_hadamard_bf16_cuda
     const int st = hadamard_quantize_a8_cuda_bf16(a_int8, a_scale, a_int_row_sum, x, K, M, block, stream);
     qb_tl_dependent_quantiser = false;
     if (st != QB200_OK) return st;
-    tl_dependent_launch = true;
+    tl_dependent_launch = dep;
     const int st2 = fused_matmul_dequantize_a8_int4t_bf16_cuda(mat_d, a_int8, w_int_packed, a_int_row_sum, w_add, a_scale,
                                                                w_scale, M, K, N, stream);
     tl_dependent_launch = false;

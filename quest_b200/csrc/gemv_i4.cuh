@@ -30,7 +30,6 @@ template <int MR, int C, bool FUSED>
 __global__ void __launch_bounds__(gemv::kThreads)
 gemv_i4_kernel(const uint8_t* __restrict__ A, const uint8_t* __restrict__ B, const EpilogueParams ep, const int M,
                const int N, const int K) {
-    let_dependents_launch();
     extern __shared__ uint4 gemv_sA[];  // [MR][K / 32] chunks of 16 packed bytes
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int chunks = K >> 5;          // 32 codes = 16 bytes per chunk

@@ -240,14 +240,19 @@ int w4a4_linear_hadamard_a8_bf16_cuda(void* mat_d, const void* x, const void* w_
                                       int K, int N, int block, cudaStream_t stream);
 
 /*
- * State of the calling host thread; returns the previous value.  While on, every GEMM kernel this thread launches
- * through the fused entry points (fused_matmul_dequantize_*) carries a programmatic dependency on the kernel before it
- * in its stream, exactly as inside w4a4_linear_hadamard_bf16_cuda: the GEMM reads its weights (mat_b) before it waits on
- * the device for that kernel, everything else after.  The caller promises that the preceding kernel does not write
- * mat_b.  The package's column-sharded layer turns it on around the GEMM that follows its quantiser.  No counterpart in
- * the reference.
+ * Layer mode, a state of the calling host thread.  Between quest_b200_begin_layer and quest_b200_end_layer the calls
+ * hadamard_quantize_int4_cuda_bf16 / hadamard_quantize_a8_cuda_bf16 followed by a fused GEMM entry point
+ * (fused_matmul_dequantize_*) launch their kernels as the one-call layer entry points above do - those are exactly
+ * begin, the two calls, end: with programmatic dependencies where that was measured faster (the tcgen05 quantiser behind
+ * the kernel before it and the GEMM behind that quantiser; behind the small CUDA-core quantiser only the GEMM, and only
+ * below 3 M activation elements).  The GEMM then reads its weights (mat_b) before it waits on the device for the kernel
+ * before it: the caller promises that between begin and end nothing else is launched into the stream between the
+ * quantiser and the GEMM.  The package's column-sharded layer uses the pair around its quantiser and its push GEMM.
+ * QB200_DEPENDENT_LAUNCH=0..3 in the environment forces the launches (bit 0 GEMM, bit 1 quantiser dependent).  No
+ * counterpart in the reference.
  */
-int quest_b200_set_dependent_gemm_launch(int on);
+int quest_b200_begin_layer(void);
+int quest_b200_end_layer(void);
 
 /*
  * out = bf16(H_block . x) blockwise along the last dimension (out may alias x).

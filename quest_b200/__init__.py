@@ -313,17 +313,17 @@ def w4a4_linear_hadamard(
     return out
 
 
-class dependent_gemm_launch:
-    """Context manager: fused GEMMs launched by this thread inside it start behind the preceding kernel of their stream
-    with a programmatic dependency (they read their weights first and wait on the device before anything else), as the
-    one-call layer does.  Only around a GEMM whose preceding kernel does not write its weights."""
+class layer_launches:
+    """Context manager: inside it a Hadamard+quantise call followed by a fused GEMM call of this thread are launched as
+    one layer, with programmatic dependencies where the library found them faster (what the one-call layer entry points
+    do).  Nothing else may be launched into the stream between the two calls."""
 
     def __enter__(self):
-        self._prev = _lib.load().quest_b200_set_dependent_gemm_launch(1)
+        _lib.load().quest_b200_begin_layer()
         return self
 
     def __exit__(self, *exc):
-        _lib.load().quest_b200_set_dependent_gemm_launch(self._prev)
+        _lib.load().quest_b200_end_layer()
         return False
 
 

@@ -32,7 +32,8 @@ SIGNATURES = {
     "silu_mul_hadamard_quantize_int4_cuda_bf16": [_P, _P, _P, _P, _P, _I, _I, _I, _P],
     "fused_matmul_dequantize_a8_int4t_bf16_cuda": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     "quest_b200_prefers_a8": [_I, _I, _I],
-    "quest_b200_set_dependent_gemm_launch": [_I],
+    "quest_b200_begin_layer": [],
+    "quest_b200_end_layer": [],
     "hadamard_transform_cuda_bf16": [_P, _P, _I, _I, _I, _I, _P],
     "quest_b200_test_bounded_wait_cuda": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _LL, _P],
     "quest_b200_device_status": [ctypes.POINTER(ctypes.c_int)],

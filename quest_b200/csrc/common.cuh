@@ -54,6 +54,10 @@ inline cudaError_t launch_kernel_dep(bool dependent, Kernel kernel, long long gr
 // Set (per host thread) by the one-call layer entry points around their quantiser call: the tcgen05 quantiser kernel
 // (which waits on the device) is then launched with a programmatic dependency.
 extern thread_local bool qb_tl_dependent_quantiser;
+// Which kernel the last hadamard_quantize_int4_cuda_bf16 call of this host thread launched (the one-call layer decides
+// by it how to launch its GEMM).
+constexpr int kQuantiserTc = 1, kQuantiserMma = 2;
+extern thread_local int qb_tl_quantiser_kernel;
 
 // Reads and clears the device status word of the row-kernel translation unit (see tcgen05.cuh).
 int hq_tc_fetch_and_clear_device_status(int* out);

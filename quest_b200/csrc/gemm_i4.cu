@@ -1404,8 +1404,8 @@ static int pick_tile(int M, int N, int K, int sms, long long* est_cycles) {
 
 // static_splits < 0: the ordinary entry points (split-K scratch from the per-device buffer).  static_splits >= 0: the
 // entry point that allocates nothing (scratch in the static array; 0 = the library's choice of K ranges, n = n ranges).
-static int run_gemm(bool fused, const EpilogueParams& ep_in, const void* a, const void* b, int M, int K, int N,
-                    cudaStream_t stream, int static_splits = -1) {
+static int run_gemm_impl(bool fused, const EpilogueParams& ep_in, const void* a, const void* b, int M, int K, int N,
+                         cudaStream_t stream, int static_splits) {
     if (M < 0 || N < 0 || K < 0) return QB200_ERR_INVALID_ARGUMENT;
     if (M == 0 || N == 0) return QB200_OK;
     if (ep_in.out == nullptr || a == nullptr || b == nullptr) return QB200_ERR_INVALID_ARGUMENT;
@@ -1508,6 +1508,43 @@ static int run_gemm(bool fused, const EpilogueParams& ep_in, const void* a, cons
 
 using namespace qb;
 
+
+// ---- layer mode ---------------------------------------------------------------------------------------------------
+// Between quest_b200_begin_layer and quest_b200_end_layer (host-thread state; the one-call layer entry points use the
+// same two calls) the Hadamard+quantise entry point and the fused GEMM entry points launch their kernels as one layer:
+// which of the two kernels carries a programmatic dependency follows what was measured (layers back to back, 20 in a
+// CUDA graph):
+//  * from 3 M activation elements on the quantiser is the tcgen05 kernel where it can tile K, launched behind whatever
+//    kernel precedes the layer (it executes griddepcontrol.wait before its first access to global memory, so this is
+//    safe behind any kernel; behind one of this library's GEMMs its blocks are scheduled as the GEMM's leave), and the
+//    GEMM is launched behind it: -1 ... -2 us per layer;
+//  * below that the quantiser is the small CUDA-core kernel in plain stream order and only the GEMM is dependent (its
+//    set-up and first weight requests overlap the quantiser): -1.5 us per layer at M = 64 ... 512, K = 4096;
+//  * a GEMM launched that way behind the CUDA-core quantiser of a large input measured slower (+1 ... +10 us at 4 M
+//    elements and more), so where the tcgen05 kernel cannot tile K both launches stay plain.
+// QB200_DEPENDENT_LAUNCH in the environment (tests, tuning) forces the launches instead: bit 0 = the GEMM, bit 1 = the
+// quantiser is launched with a programmatic dependency; 0 = both in plain stream order.
+static thread_local bool tl_layer_mode = false;
+
+static int dependent_launch_mask() {
+    const char* e = getenv("QB200_DEPENDENT_LAUNCH");
+    return e == nullptr ? -1 : atoi(e);
+}
+
+static int run_gemm(bool fused, const EpilogueParams& ep, const void* a, const void* b, int M, int K, int N,
+                    cudaStream_t stream, int static_splits = -1) {
+    if (tl_layer_mode) {  // the kernel before this GEMM in the stream is the layer's quantiser
+        const int mask = dependent_launch_mask();
+        const bool small = (long long)M * K < 3ll * 1024 * 1024;
+        tl_dependent_launch = mask >= 0 ? (mask & 1) != 0
+                                        : (qb_tl_quantiser_kernel == kQuantiserTc || (qb_tl_quantiser_kernel == kQuantiserMma && small));
+        qb_tl_quantiser_kernel = 0;  // consumed: a second GEMM of the layer follows a GEMM, not the quantiser
+    }
+    const int st = run_gemm_impl(fused, ep, a, b, M, K, N, stream, static_splits);
+    tl_dependent_launch = false;
+    return st;
+}
+
 extern "C" int matmul_int4_int4t_int32_cuda(void* mat_c, const void* mat_a, const void* mat_b, int M, int K, int N,
                                             cudaStream_t stream) {
     EpilogueParams ep{};
@@ -1574,7 +1611,14 @@ extern "C" int fused_matmul_dequantize_a8_int4t_bf16_cuda(void* mat_d, const voi
     int dev = 0;
     const int sms = sm_count_of_current_device(&dev);
     if (sms <= 0) return QB200_ERR_CUDA;
-    return launch_gemm_wide_a8(ep, mat_a8, mat_b, M, K, N, sms, dev, stream);
+    if (tl_layer_mode) {  // behind the layer's tcgen05 quantiser: dependent unless the environment says otherwise
+        const int mask = dependent_launch_mask();
+        tl_dependent_launch = mask < 0 || (mask & 1) != 0;
+        qb_tl_quantiser_kernel = 0;
+    }
+    const int st = launch_gemm_wide_a8(ep, mat_a8, mat_b, M, K, N, sms, dev, stream);
+    tl_dependent_launch = false;
+    return st;
 }
 
 constexpr bool kA8ByDefault = true;  // measured faster wherever the 256 x 256 kernel and the tcgen05 quantiser both apply (QB200_A8=0 switches it off)
@@ -1619,31 +1663,33 @@ extern "C" int fused_matmul_dequantize_int4_int4t_bf16_cuda(void* mat_d, const v
 
 extern "C" int hadamard_quantize_int4_cuda_bf16(void*, void*, void*, const void*, int, int, int, cudaStream_t);
 
-// QB200_DEPENDENT_LAUNCH=0 in the environment: the one-call layer launches its two kernels in plain stream order.
-static bool dependent_launches_enabled() {
-    const char* e = getenv("QB200_DEPENDENT_LAUNCH");
-    return e == nullptr || e[0] != '0';
+extern "C" int quest_b200_begin_layer(void) {
+    const int mask = dependent_launch_mask();
+    tl_layer_mode = true;
+    qb_tl_dependent_quantiser = mask < 0 || (mask & 2) != 0;
+    qb_tl_quantiser_kernel = 0;
+    return QB200_OK;
+}
+
+extern "C" int quest_b200_end_layer(void) {
+    tl_layer_mode = false;
+    qb_tl_dependent_quantiser = false;
+    qb_tl_quantiser_kernel = 0;
+    tl_dependent_launch = false;
+    return QB200_OK;
 }
 
 extern "C" int w4a4_linear_hadamard_bf16_cuda(void* mat_d, const void* x, const void* w_int_packed, const void* w_add,
                                               const void* w_scale, void* a_int_packed, void* a_scale, void* a_int_row_sum,
                                               int M, int K, int N, int block, cudaStream_t stream) {
     if (!a_int_row_sum) return QB200_ERR_INVALID_ARGUMENT;
-    // The quantiser, too, is launched with a programmatic dependency (on whatever kernel precedes the layer in the
-    // stream): it executes griddepcontrol.wait before its first access to global memory, so this is safe behind any
-    // kernel, and behind one of this library's GEMMs (layers back to back) its blocks are scheduled as the GEMM's leave.
-    const bool dep = dependent_launches_enabled();
-    qb_tl_dependent_quantiser = dep;
-    const int st = hadamard_quantize_int4_cuda_bf16(a_int_packed, a_scale, a_int_row_sum, x, K, M, block, stream);
-    qb_tl_dependent_quantiser = false;
-    if (st != QB200_OK) return st;
-    // The GEMM kernel is launched with a programmatic dependency: it starts while the quantiser's last blocks still
-    // run, sets itself up, requests its first weights and waits for the quantiser on the device (see tl_dependent_launch).
-    tl_dependent_launch = dep;
-    const int st2 = fused_matmul_dequantize_int4_int4t_bf16_cuda(mat_d, a_int_packed, w_int_packed, a_int_row_sum, w_add,
-                                                                 a_scale, w_scale, M, K, N, stream);
-    tl_dependent_launch = false;
-    return st2;
+    quest_b200_begin_layer();
+    int st = hadamard_quantize_int4_cuda_bf16(a_int_packed, a_scale, a_int_row_sum, x, K, M, block, stream);
+    if (st == QB200_OK)
+        st = fused_matmul_dequantize_int4_int4t_bf16_cuda(mat_d, a_int_packed, w_int_packed, a_int_row_sum, w_add, a_scale,
+                                                          w_scale, M, K, N, stream);
+    quest_b200_end_layer();
+    return st;
 }
 
 extern "C" int hadamard_quantize_a8_cuda_bf16(void*, void*, void*, const void*, int, int, int, cudaStream_t);
@@ -1652,22 +1698,13 @@ extern "C" int w4a4_linear_hadamard_a8_bf16_cuda(void* mat_d, const void* x, con
                                                  const void* w_scale, void* a_int8, void* a_scale, void* a_int_row_sum,
                                                  int M, int K, int N, int block, cudaStream_t stream) {
     if (!a_int_row_sum) return QB200_ERR_INVALID_ARGUMENT;
-    const bool dep = dependent_launches_enabled();
-    qb_tl_dependent_quantiser = dep;  // see w4a4_linear_hadamard_bf16_cuda
-    const int st = hadamard_quantize_a8_cuda_bf16(a_int8, a_scale, a_int_row_sum, x, K, M, block, stream);
-    qb_tl_dependent_quantiser = false;
-    if (st != QB200_OK) return st;
-    tl_dependent_launch = dep;
-    const int st2 = fused_matmul_dequantize_a8_int4t_bf16_cuda(mat_d, a_int8, w_int_packed, a_int_row_sum, w_add, a_scale,
-                                                               w_scale, M, K, N, stream);
-    tl_dependent_launch = false;
-    return st2;
-}
-
-extern "C" int quest_b200_set_dependent_gemm_launch(int on) {
-    const int prev = tl_dependent_launch ? 1 : 0;
-    tl_dependent_launch = on != 0;
-    return prev;
+    quest_b200_begin_layer();  // the quantiser of this route is always the tcgen05 kernel: both launches dependent
+    int st = hadamard_quantize_a8_cuda_bf16(a_int8, a_scale, a_int_row_sum, x, K, M, block, stream);
+    if (st == QB200_OK)
+        st = fused_matmul_dequantize_a8_int4t_bf16_cuda(mat_d, a_int8, w_int_packed, a_int_row_sum, w_add, a_scale, w_scale,
+                                                        M, K, N, stream);
+    quest_b200_end_layer();
+    return st;
 }
 
 extern "C" int quest_b200_test_bounded_wait_cuda(void* mat_d, const void* mat_a, const void* mat_b, const void* vec_a_add,

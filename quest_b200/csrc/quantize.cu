@@ -17,6 +17,7 @@
 namespace qb {
 
 thread_local bool qb_tl_dependent_quantiser = false;
+thread_local int qb_tl_quantiser_kernel = 0;
 
 struct RowParams {
     const __nv_bfloat16* x;        // [M,K] input
@@ -1004,9 +1005,14 @@ extern "C" int hadamard_quantize_int4_cuda_bf16(void* x_int_packed_ptr, void* sc
     // Tensor-core kernel where the shape fits its tiling; QB200_HQ_KERNEL=mma|tc forces one (tests, tuning).
     const char* force = getenv("QB200_HQ_KERNEL");
     // Measured crossover: below ~12 M elements the launch is one short wave and the CUDA-core kernel's smaller
-    // set-up wins by about a microsecond.
-    const bool want_tc = force != nullptr ? (force[0] == 't') : ((long long)p.M * p.K >= 12ll * 1024 * 1024);
+    // set-up wins by about a microsecond.  Inside the one-call layer the crossover is 3 M elements: there the tcgen05
+    // kernel and the GEMM behind it are launched with programmatic dependencies, which gains more than that
+    // microsecond (M = 1024, K = N = 4096: 27.2 against 28.2 us per layer), while a GEMM launched that way behind
+    // the CUDA-core kernel measured slower from 4 M elements on (29.5 us).
+    const long long tc_from = qb_tl_dependent_quantiser ? 3ll * 1024 * 1024 : 12ll * 1024 * 1024;
+    const bool want_tc = force != nullptr ? (force[0] == 't') : ((long long)p.M * p.K >= tc_from);
     if (want_tc && hq_tc_eligible(p, block)) {
+        qb_tl_quantiser_kernel = kQuantiserTc;
         switch (block) {
             case 64: return launch_hq_tc<64>(p, stream);
             case 128: return launch_hq_tc<128>(p, stream);
@@ -1014,6 +1020,7 @@ extern "C" int hadamard_quantize_int4_cuda_bf16(void* x_int_packed_ptr, void* sc
         }
     }
     if (force != nullptr && force[0] == 't') return QB200_ERR_UNSUPPORTED;
+    qb_tl_quantiser_kernel = kQuantiserMma;
     switch (block) {
         case 64: return launch_hq_mma<64>(p, stream);
         case 128: return launch_hq_mma<128>(p, stream);

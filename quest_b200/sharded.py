@@ -78,9 +78,8 @@ class ShardedLinear4bit:
         self.quantize_activations(x, ws)
         if self._stage is not None:
             self._stage("quantised")
-        with quest.dependent_gemm_launch():
-            quest.fused_matmul_dequantize_int4_int4t_bf16_into(ws["a_int_packed"], self.w_int_packed, ws["a_int_row_sum"],
-                                                               self.w_add, ws["a_scale"], self.w_scale, out_cols)
+        quest.fused_matmul_dequantize_int4_int4t_bf16_into(ws["a_int_packed"], self.w_int_packed, ws["a_int_row_sum"],
+                                                           self.w_add, ws["a_scale"], self.w_scale, out_cols)
 
     def quantize_activations(self, x: torch.Tensor, ws: dict) -> None:
         if self.use_hadamard:
@@ -143,9 +142,11 @@ class ShardedLinear4bit:
         if self.exchange == "push":
             t, hdl, ptrs, views = ws["symm"][ws["parity"]]
             ws["parity"] ^= 1
-            self.quantize_activations(x, ws)
-            stage("quantised")
-            if m <= self.SMALL_M and views is not None:
+            small = m <= self.SMALL_M and views is not None
+            if small or not self.use_hadamard:
+                self.quantize_activations(x, ws)
+                stage("quantised")
+            if small:
                 # Few rows: the weight-streaming kernels (dp4a, split-K) are several times faster than a tensor-core
                 # tile kernel that walks K serially, and the block to deliver is tiny - compute it into the local buffer
                 # and copy it into every peer's.
@@ -157,7 +158,16 @@ class ShardedLinear4bit:
             else:
                 off = self.n0 * t.element_size()
                 order = [self.rank] + [(self.rank + i) % self.world for i in range(1, self.world)]
-                with quest.dependent_gemm_launch():  # the GEMM sets itself up and fetches weights behind the quantiser
+                if self.use_hadamard:
+                    # quantiser and push GEMM as one layer: the GEMM sets itself up and requests its first weights while the
+                    # quantiser's last blocks run, and the quantiser starts while the kernel before it drains
+                    with quest.layer_launches():
+                        self.quantize_activations(x, ws)
+                        stage("quantised")
+                        quest.fused_matmul_dequantize_int4_int4t_bf16_push(
+                            ws["a_int_packed"], self.w_int_packed, ws["a_int_row_sum"], self.w_add, ws["a_scale"], self.w_scale,
+                            [ptrs[r] + off for r in order], self.n_total)
+                else:
                     quest.fused_matmul_dequantize_int4_int4t_bf16_push(
                         ws["a_int_packed"], self.w_int_packed, ws["a_int_row_sum"], self.w_add, ws["a_scale"], self.w_scale,
                         [ptrs[r] + off for r in order], self.n_total)

@@ -347,8 +347,9 @@ def test_one_call_layer_equals_the_two_op_route(m, k, n):
     x = make_activations("student", m, k, seed=m + k).to(DEV)
     w = (0.02 * torch.randn(n, k, generator=torch.Generator().manual_seed(n))).to(torch.bfloat16).to(DEV)
     wp, ws, wa, _ = quest.preprocess_weight(w, use_hadamard=True)
-    p_ref, s_ref, r_ref = quest.hadamard_quantize_int4(x)
-    y_ref = quest.fused_matmul_dequantize_int4_int4t_bf16(p_ref, wp, r_ref, wa, s_ref, ws)
+    with quest.layer_launches():  # the same choice of quantiser kernel as inside the one call (tcgen05 from 3 M elements on)
+        p_ref, s_ref, r_ref = quest.hadamard_quantize_int4(x)
+        y_ref = quest.fused_matmul_dequantize_int4_int4t_bf16(p_ref, wp, r_ref, wa, s_ref, ws)
     pk = torch.zeros(m, k // 2, dtype=torch.uint8, device=DEV)
     sc = torch.zeros(m, 1, dtype=torch.bfloat16, device=DEV)
     rs = torch.zeros(m, 1, dtype=torch.int32, device=DEV)
@@ -370,8 +371,10 @@ def test_one_call_layer_equals_the_two_op_route(m, k, n):
     out.zero_()
     graph.replay()
     torch.cuda.synchronize()
-    p2, s2, r2 = quest.hadamard_quantize_int4(x2)
-    assert out.equal(quest.fused_matmul_dequantize_int4_int4t_bf16(p2, wp, r2, wa, s2, ws)) and pk.equal(p2)
+    with quest.layer_launches():
+        p2, s2, r2 = quest.hadamard_quantize_int4(x2)
+        y2 = quest.fused_matmul_dequantize_int4_int4t_bf16(p2, wp, r2, wa, s2, ws)
+    assert out.equal(y2) and pk.equal(p2)
 
 
 # ------------------------------------------------------------------ balanced tile columns (int8-operand GEMM) ---

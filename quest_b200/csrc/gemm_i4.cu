@@ -1634,6 +1634,10 @@ extern "C" int quest_b200_prefers_a8(int M, int K, int N) {
     const int sms = sm_count_of_current_device(&dev);
     long long est = 0;
     if (sms <= 0 || pick_tile(M, N, K, sms, &est) != kWideTile) return 0;
+    // The int8 operand is twice the packed one.  Up to 32 MB (M = 8192, K = 4096) the route measured 1-5 % faster, at
+    // 64 MB the same, beyond that slower (M = 65536, K = 4096: 889 against 791 us): the operand no longer stays in L2
+    // between the CTAs that share its rows.
+    if ((long long)M * K > (48ll << 20)) return 0;
     return hq_tc_shape_ok(K) ? 1 : 0;
 }
 

@@ -281,7 +281,8 @@ def check_exchange_parity(layer, x, n_local: int, block: int, exchanges, dev) ->
         if ok.item() == 0:
             delivered.pop(exch, None)
     torch.cuda.synchronize()
-    pa, sa, ra = quest.hadamard_quantize_int4(x, block)
+    with quest.layer_launches():  # the quantiser kernel the layer itself chooses for this size
+        pa, sa, ra = quest.hadamard_quantize_int4(x, block)
     for s in range(world):
         w_s = synthetic_weight(n_local, k, 1000 + s).to(dev)
         wp, ws, wa, _ = quest.preprocess_weight(w_s, use_hadamard=True, block=block)
@@ -884,6 +885,8 @@ def run_c4(args):
                     row["nvlink_floor_us"] = recv / 770e9 * 1e6
                     del lay
                 torch.cuda.synchronize()
+                with quest.layer_launches():  # the quantiser kernel the layer itself chooses for this size
+                    quest.hadamard_quantize_int4(x, args.block, pk, sc, rs)
                 equal = bool(delivered)
                 for s in range(world):
                     a, b = shard_bounds(n_total, s, world)

@@ -15,6 +15,8 @@ Two exchange modes:
 """
 from __future__ import annotations
 
+import contextlib
+
 import torch
 import torch.distributed as dist
 
@@ -75,11 +77,13 @@ class ShardedLinear4bit:
         return other
 
     def compute_shard(self, x: torch.Tensor, out_cols: torch.Tensor, ws: dict) -> None:
-        self.quantize_activations(x, ws)
-        if self._stage is not None:
-            self._stage("quantised")
-        quest.fused_matmul_dequantize_int4_int4t_bf16_into(ws["a_int_packed"], self.w_int_packed, ws["a_int_row_sum"],
-                                                           self.w_add, ws["a_scale"], self.w_scale, out_cols)
+        # quantiser and GEMM as one layer (same choice of quantiser kernel and of dependent launches as linear_forward)
+        with quest.layer_launches() if self.use_hadamard else contextlib.nullcontext():
+            self.quantize_activations(x, ws)
+            if self._stage is not None:
+                self._stage("quantised")
+            quest.fused_matmul_dequantize_int4_int4t_bf16_into(ws["a_int_packed"], self.w_int_packed, ws["a_int_row_sum"],
+                                                               self.w_add, ws["a_scale"], self.w_scale, out_cols)
 
     def quantize_activations(self, x: torch.Tensor, ws: dict) -> None:
         if self.use_hadamard:
@@ -143,16 +147,14 @@ class ShardedLinear4bit:
             t, hdl, ptrs, views = ws["symm"][ws["parity"]]
             ws["parity"] ^= 1
             small = m <= self.SMALL_M and views is not None
-            if small or not self.use_hadamard:
-                self.quantize_activations(x, ws)
-                stage("quantised")
             if small:
                 # Few rows: the weight-streaming kernels (dp4a, split-K) are several times faster than a tensor-core
                 # tile kernel that walks K serially, and the block to deliver is tiny - compute it into the local buffer
                 # and copy it into every peer's.
                 mine = t[:, self.n0:self.n1]
-                quest.fused_matmul_dequantize_int4_int4t_bf16_into(ws["a_int_packed"], self.w_int_packed, ws["a_int_row_sum"],
-                                                                   self.w_add, ws["a_scale"], self.w_scale, mine)
+                self._stage = stage
+                self.compute_shard(x, mine, ws)
+                self._stage = None
                 for i in range(1, self.world):
                     views[(self.rank + i) % self.world][:, self.n0:self.n1].copy_(mine)
             else:
@@ -168,6 +170,8 @@ class ShardedLinear4bit:
                             ws["a_int_packed"], self.w_int_packed, ws["a_int_row_sum"], self.w_add, ws["a_scale"], self.w_scale,
                             [ptrs[r] + off for r in order], self.n_total)
                 else:
+                    self.quantize_activations(x, ws)
+                    stage("quantised")
                     quest.fused_matmul_dequantize_int4_int4t_bf16_push(
                         ws["a_int_packed"], self.w_int_packed, ws["a_int_row_sum"], self.w_add, ws["a_scale"], self.w_scale,
                         [ptrs[r] + off for r in order], self.n_total)

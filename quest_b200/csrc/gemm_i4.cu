@@ -108,6 +108,7 @@ struct EpilogueParams {
     int slab_ints;          // slab_rows * 256: a slab holds only the rows a tile can have (M rounded up to 8, at most 128)
     int* counters;          // one per output tile, all zero between launches
     int tma_store;          // 256 x 256 kernel, fused: the output tensor map is valid (the last tile leaves as bulk tensor stores)
+    int tma_store16;        // int8-operand variant: the 16-column output map is valid too (earlier tiles leave as small bulk stores)
     int test_skip_producer; // tests only: the TMA producer issues nothing, so that every bounded wait of the launch runs out
     // 256-row kernel: the N range is cut into col_count tile columns whose widths are multiples of 16, at most 256; the
     // first col_rem of them are (col_units + 1) * 16 wide, the others col_units * 16 (col_units = 16, col_rem = 0: all 256)
@@ -666,6 +667,8 @@ __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bul
 // on their own, at the latest when the grid ends): enough to let the CTA go.
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// At most the newest bulk group of this thread may still be reading its shared-memory source.
+__device__ __forceinline__ void bulk_wait_read_but_one() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 
 // One warp's share of a 256 x 256 tile: its 32 rows (tensor-memory lanes) x the columns [c_begin, c_end), in pieces of 64.
 // stage_base == 0: every thread stores its row's results itself (32-byte pieces).  stage_base != 0 (fused output, the
@@ -686,7 +689,51 @@ __device__ __forceinline__ void wide_convert_columns(const EpilogueParams& ep, c
                                                      const CUtensorMap* peer_maps, int n_peer_maps, uint32_t t_row,
                                                      int row, bool row_ok, int a_add, float half_a_mul, const int* sb_add,
                                                      const float* sb_mul, int n0, int N, int c_begin, int c_end,
-                                                     uint32_t stage_base, int warp_row0, int lane) {
+                                                     uint32_t stage_base, int warp_row0, int lane,
+                                                     const CUtensorMap* tmap_d16 = nullptr, uint32_t mini_base = 0,
+                                                     uint32_t* mini_count = nullptr) {
+    if (FUSED && mini_base != 0) {
+        // A tile that is not the CTA's last one (int8-operand variant): the rings belong to the next tile already, but
+        // 16 KB of shared memory are free there - two 1 KB slabs per epilogue warp.  The warp writes 32 rows x 16
+        // columns of bf16 (dense rows of 32 bytes) into one slab while the bulk store of the other is still being
+        // read, so the stores leave through the copy engine behind the arithmetic instead of occupying the warp's store
+        // path (about 3 us per tile), and tensor memory is released for the next tile's MMAs as soon as it has been
+        // read.  Rows and columns outside the matrix are clipped by the tensor map.
+        uint32_t piece = *mini_count;
+#pragma unroll 1
+        for (int c0 = c_begin; c0 < c_end; c0 += 64) {
+            if (n0 + c0 >= N) break;  // warp-uniform
+            uint32_t r0[32], r1[32];
+            tmem_ld32(t_row + c0, r0);
+            tmem_ld32(t_row + c0 + 32, r1);
+            tmem_ld_wait();
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                if (c0 + 32 * h >= c_end) break;  // widths are multiples of 16: a tile may end inside a chunk
+                uint32_t w[16];
+                dequant_chunk(h == 0 ? r0 : r1, a_add, half_a_mul, sb_add + c0 + 32 * h, sb_mul + c0 + 32 * h, w);
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    const int c = c0 + 32 * h + 16 * q;
+                    if (c >= c_end) break;
+                    const uint32_t slab = mini_base + (piece & 1u) * 1024u;
+                    if (lane == 0) bulk_wait_read_but_one();  // the store that used this slab two pieces ago has read it
+                    __syncwarp();
+                    sts128(slab + lane * 32, make_uint4(w[8 * q], w[8 * q + 1], w[8 * q + 2], w[8 * q + 3]));
+                    sts128(slab + lane * 32 + 16, make_uint4(w[8 * q + 4], w[8 * q + 5], w[8 * q + 6], w[8 * q + 7]));
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(tmap_d16, slab, n0 + c, warp_row0);
+                        bulk_commit_group();
+                    }
+                    ++piece;
+                }
+            }
+        }
+        *mini_count = piece;
+        return;
+    }
 #pragma unroll 1
     for (int cx = c_begin; cx < c_end; cx += 64) {
         // a tile width that is no multiple of 64: the last piece starts earlier and rewrites columns of the one before
@@ -739,8 +786,9 @@ __device__ __forceinline__ void wide_convert_columns(const EpilogueParams& ep, c
 template <bool FUSED, bool PUSH, bool A8 = false>
 __global__ void __launch_bounds__(PUSH ? wide::kThreads : (A8 ? wide::kThreads - 32 : wide::kThreads - 32 * wide::kPushWarps), 1)
 gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                    const __grid_constant__ CUtensorMap tmap_d, const __grid_constant__ PeerMaps<PUSH> peers,
-                    const __grid_constant__ EpilogueParams ep, const int M, const int N, const int K) {
+                    const __grid_constant__ CUtensorMap tmap_d, const __grid_constant__ CUtensorMap tmap_d16,
+                    const __grid_constant__ PeerMaps<PUSH> peers, const __grid_constant__ EpilogueParams ep, const int M,
+                    const int N, const int K) {
     using namespace wide;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_base = smem_u32(smem_raw);
@@ -905,7 +953,7 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         uint8_t* vec_ptr = smem_raw + (vec_base - raw_base);
         int* sb_add = reinterpret_cast<int*>(vec_ptr);
         float* sb_mul = reinterpret_cast<float*>(vec_ptr + TN * 4);
-        uint32_t local_tile = 0;
+        uint32_t local_tile = 0, mini_pieces = 0;
         bool ok = true;
         if (A8) wait_for_preceding_grid();  // the row sums and scales come from the quantiser
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
@@ -942,9 +990,14 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const bool last = tile + (int)gridDim.x >= num_tiles;
             const bool staged = FUSED && last && ep.tma_store;
             const uint32_t stage_base = staged ? u_base + (uint32_t)(half * 4 + quad) * 16384u : 0u;
+            // int8-operand variant, earlier tiles: the 16 KB behind the third A slot hold two 1 KB slabs per epilogue warp
+            const uint32_t mini_base = (A8 && FUSED && !staged && ep.tma_store16)
+                                           ? p_base + (uint32_t)(P_STAGES * (TN * PK_ROW) + TM * U8_ROW) + (uint32_t)(warp - kFirstEpi) * 2048u
+                                           : 0u;
             if (m0 + half * 128 < M)  // warp-uniform: otherwise this accumulator was not computed
                 wide_convert_columns<FUSED>(ep, &tmap_d, peers.m, PUSH ? ep.n_peer : 0, t_row, row, row_ok, a_add, half_a_mul,
-                                            sb_add, sb_mul, n0, N, 0, bn, stage_base, m0 + half * 128 + quad * 32, lane);
+                                            sb_add, sb_mul, n0, N, 0, bn, stage_base, m0 + half * 128 + quad * 32, lane,
+                                            &tmap_d16, mini_base, &mini_pieces);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tmem_empty);
@@ -1243,6 +1296,20 @@ static int encode_output_map(CUtensorMap* map, void* base, long long ld, int M, 
                ? QB200_OK : QB200_ERR_DRIVER;
 }
 
+// The same output as 32-row x 16-column boxes of dense 32-byte rows (no swizzle): what an epilogue warp of the
+// int8-operand variant stores per piece of a tile that is not its CTA's last one.
+static int encode_output_map16(CUtensorMap* map, void* base, long long ld, int M, int N) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (fn == nullptr) return QB200_ERR_DRIVER;
+    const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {16, 32};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS
+               ? QB200_OK : QB200_ERR_DRIVER;
+}
+
 template <bool PUSH>
 static void make_output_maps(CUtensorMap* map, PeerMaps<PUSH>* peers, EpilogueParams* ep, int M, int N) {
     memset(map, 0, sizeof(*map));
@@ -1312,10 +1379,16 @@ static int launch_gemm_wide_a8(const EpilogueParams& ep_in, const void* a8, cons
     CUtensorMap md;
     PeerMaps<false> peers;
     make_output_maps<false>(&md, &peers, &ep, M, N);
+    CUtensorMap md16;
+    memset(&md16, 0, sizeof(md16));
+    ep.tma_store16 = 0;
+    if (ep.tma_store && encode_output_map16(&md16, ep.out, ep.ld, M, N) == QB200_OK) ep.tma_store16 = 1;
+    if (const char* e = getenv("QB200_GEMM_TMA_STORE"))
+        if (e[0] == '1') ep.tma_store16 = 0;  // 1: only the last tile of a CTA leaves through shared memory
     wide_columns(&ep, M, N, sms, true);
     const int tiles = ((M + wide::TM - 1) / wide::TM) * ep.col_count;
     const int grid = tiles < sms ? tiles : sms;
-    if (launch_kernel(kernel, grid, wide::kThreads - 32, wide::SMEM_BYTES, stream, ma, mb, md, peers, ep, M, N, K) != cudaSuccess) {
+    if (launch_kernel(kernel, grid, wide::kThreads - 32, wide::SMEM_BYTES, stream, ma, mb, md, md16, peers, ep, M, N, K) != cudaSuccess) {
         cudaGetLastError();
         return QB200_ERR_CUDA;
     }
@@ -1350,7 +1423,7 @@ static int launch_gemm_wide_impl(const EpilogueParams& ep_in, const void* a, con
         memset(&md, 0, sizeof(md));
         memset(&peers, 0, sizeof(peers));
     }
-    if (launch_kernel(kernel, grid, threads, wide::SMEM_BYTES, stream, ma, mb, md, peers, ep, M, N, K) != cudaSuccess) {
+    if (launch_kernel(kernel, grid, threads, wide::SMEM_BYTES, stream, ma, mb, md, md, peers, ep, M, N, K) != cudaSuccess) {
         cudaGetLastError();
         return QB200_ERR_CUDA;
     }

@@ -409,6 +409,12 @@ def test_int8_operand_gemm_with_balanced_tile_columns(m, k, n, monkeypatch):
         monkeypatch.setenv("QB200_GEMM_BALANCE", "0")
         assert quest.fused_matmul_dequantize_a8(a8, wp, a_add, b_add, a_mul, b_mul).equal(ref)
         monkeypatch.delenv("QB200_GEMM_BALANCE")
+        # every way a tile can leave: 16-column bulk stores for a CTA's earlier tiles and 64-column ones for its last
+        # (default), per-thread stores for the earlier tiles (1), per-thread stores throughout (0)
+        for mode in ("1", "0"):
+            monkeypatch.setenv("QB200_GEMM_TMA_STORE", mode)
+            assert quest.fused_matmul_dequantize_a8(a8, wp, a_add, b_add, a_mul, b_mul).equal(ref)
+        monkeypatch.delenv("QB200_GEMM_TMA_STORE")
     assert quest.device_status() == 0
 
 

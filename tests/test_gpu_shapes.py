@@ -377,7 +377,7 @@ def test_one_call_layer_equals_the_two_op_route(m, k, n):
     assert out.equal(y2) and pk.equal(p2)
 
 
-# ------------------------------------------------------------------ balanced tile columns (int8-operand GEMM) ---
+# ------------------------------------------------------------------ balanced tile columns (256-row GEMM kernel) ---
 @pytest.mark.parametrize("m,k,n", [
     (2048, 256, 4096),    # 8 x 16 tiles of 256 columns -> 8 x 18 of 240 / 224
     (2048, 128, 4000),    # the same cut with a ragged last column
@@ -385,14 +385,18 @@ def test_one_call_layer_equals_the_two_op_route(m, k, n):
     (1900, 128, 14336),   # 8 x 56 -> 8 x 74 columns of 208 / 192, four waves, ragged last tile row
     (8192, 128, 4096),    # four tiles per CTA, every one narrower
     (1024, 256, 8192),    # 4 x 32 -> 4 x 37 columns of 224 / 208
-    (600, 128, 3000),     # too few tiles to fill the SMs with tiles of at least 192 columns: stays at 256
+    (2048, 128, 2560),    # packed operands only: 8 x 10 -> 8 x 18 columns of 144 / 128
+    (2048, 128, 5120),    # packed operands only: 8 x 20 -> 8 x 37 columns of 144 / 128, two waves
+    (600, 128, 3000),     # too few tiles to fill the SMs with tiles of at least 128 columns: stays at 256
 ])
-def test_int8_operand_gemm_with_balanced_tile_columns(m, k, n, monkeypatch):
-    """Where more, narrower tile columns fill the same number of waves over the SMs, the int8-operand GEMM cuts N into
-    columns of 192 ... 240 instead of 256 (widths multiples of 16; the last 64-column piece of a tile overlaps the one
-    before it).  Whatever the cut, the output is bit-identical to the packed route (uniform 256-column tiles), with the
-    cut switched off, and for a second launch on other data."""
+def test_gemm_with_balanced_tile_columns(m, k, n, monkeypatch):
+    """Where more, narrower tile columns fill the same number of waves over the SMs, the 256-row GEMM kernel cuts N into
+    columns of 128 ... 240 (packed operands) or 192 ... 240 (int8 operand) instead of 256 (widths multiples of 16; the last
+    64-column piece of a tile overlaps the one before it; B rows beyond the width are not unpacked).  Whatever the cut and
+    whichever way the tiles are stored, both routes give the bits of the uniform 256-column tiles with per-thread stores,
+    which in turn are the int32 product put through the epilogue in torch."""
     g = torch.Generator(device=DEV).manual_seed(m + n)
+    monkeypatch.setenv("QB200_GEMM_TILE", "512")  # the 256-row kernel at every shape (packed route)
     for rnd in range(2):
         packed = torch.randint(0, 256, (m, k // 2), dtype=torch.uint8, device=DEV, generator=g)
         wp = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device=DEV, generator=g)
@@ -402,20 +406,30 @@ def test_int8_operand_gemm_with_balanced_tile_columns(m, k, n, monkeypatch):
         b_mul = (0.01 + torch.rand(n, 1, device=DEV, generator=g)).to(torch.bfloat16)
         codes = quest.unpack_int4(packed).view(m, k // 32, 16, 2)
         a8 = (torch.cat([codes[..., 0], codes[..., 1]], dim=-1).reshape(m, k) * 16).to(torch.int8).view(torch.uint8).contiguous()
-        ref = quest.fused_matmul_dequantize_int4_int4t_bf16(packed, wp, a_add, b_add, a_mul, b_mul)
-        out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
-        quest.fused_matmul_dequantize_a8(a8, wp, a_add, b_add, a_mul, b_mul, out=out)
-        assert out.equal(ref)
         monkeypatch.setenv("QB200_GEMM_BALANCE", "0")
-        assert quest.fused_matmul_dequantize_a8(a8, wp, a_add, b_add, a_mul, b_mul).equal(ref)
+        monkeypatch.setenv("QB200_GEMM_TMA_STORE", "0")
+        ref = quest.fused_matmul_dequantize_int4_int4t_bf16(packed, wp, a_add, b_add, a_mul, b_mul)
+        acc = (quest.unpack_int4(packed).float() @ quest.unpack_int4(wp).float().t()).to(torch.int32)  # exact: |sums| < 2^24
+        want = ((2 * acc + a_add + b_add.t()).float() * (0.5 * a_mul.float() * b_mul.float().t())).to(torch.bfloat16)
+        assert ref.equal(want)
+        for balance in ("0", "1"):
+            monkeypatch.setenv("QB200_GEMM_BALANCE", balance)
+            # every way a tile can leave: per-thread stores throughout (0), 64-column bulk stores for a CTA's last tile (1),
+            # plus 16-column bulk stores for its earlier tiles on the int8-operand route (unset)
+            for store in ("0", "1", None):
+                if store is None:
+                    monkeypatch.delenv("QB200_GEMM_TMA_STORE")
+                else:
+                    monkeypatch.setenv("QB200_GEMM_TMA_STORE", store)
+                out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+                quest.fused_matmul_dequantize_int4_int4t_bf16(packed, wp, a_add, b_add, a_mul, b_mul, out)
+                assert out.equal(ref), ("packed", balance, store)
+                out.fill_(float("nan"))
+                quest.fused_matmul_dequantize_a8(a8, wp, a_add, b_add, a_mul, b_mul, out=out)
+                assert out.equal(ref), ("int8 operand", balance, store)
         monkeypatch.delenv("QB200_GEMM_BALANCE")
-        # every way a tile can leave: 16-column bulk stores for a CTA's earlier tiles and 64-column ones for its last
-        # (default), per-thread stores for the earlier tiles (1), per-thread stores throughout (0)
-        for mode in ("1", "0"):
-            monkeypatch.setenv("QB200_GEMM_TMA_STORE", mode)
-            assert quest.fused_matmul_dequantize_a8(a8, wp, a_add, b_add, a_mul, b_mul).equal(ref)
-        monkeypatch.delenv("QB200_GEMM_TMA_STORE")
     assert quest.device_status() == 0
+
 
 
 @pytest.mark.parametrize("m,k,n", [(2048, 4096, 4096), (1024, 4096, 14336), (4096, 8192, 1024)])

@@ -255,6 +255,16 @@ int quest_b200_begin_layer(void);
 int quest_b200_end_layer(void);
 
 /*
+ * Copies one block of bf16 [rows, cols] (row stride ld elements in the source and in every destination) from src to
+ * n_dst <= 7 destinations with one launch.  The column-sharded layer uses it for its few-row exchange: the block a rank
+ * has computed goes into every peer's output buffer (peer memory mapped into this address space; plain 16-byte stores).
+ * cols and ld must be multiples of 8 and every pointer 16-byte aligned (QB200_ERR_UNSUPPORTED otherwise).  No counterpart
+ * in the reference.
+ */
+int quest_b200_copy_block_to_peers_cuda(const void* src, void* const* dsts, int n_dst, int rows, int cols, long long ld,
+                                        cudaStream_t stream);
+
+/*
  * out = bf16(H_block . x) blockwise along the last dimension (out may alias x).
  * weight_side == 0: entries +-bf16(block^-0.5), the activation-side matrix of
  * gemm-quest/benchmarks/utils.py:17,89-90.  weight_side != 0: entries +-fp32(block^-0.5), the

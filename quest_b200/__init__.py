@@ -8,6 +8,8 @@ launches of the reference's ``linear_forward``) and ``hadamard_transform``.
 """
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 from . import _lib
@@ -311,6 +313,25 @@ def w4a4_linear_hadamard(
           _lib.ptr(w_scale), _lib.ptr(a_int_packed), _lib.ptr(a_scale), _lib.ptr(a_int_row_sum), m, k, n, int(block),
           _lib.stream_of(x))
     return out
+
+
+def copy_block_to_peers(src: torch.Tensor, dsts) -> bool:
+    """Copies the 2-D bf16 view ``src`` into every view of ``dsts`` (same shape and strides; typically the same column
+    block of the peers' output buffers) with one kernel launch.  Returns False, having copied nothing, where the views
+    are not made of whole 16-byte pieces (the caller then copies them one by one)."""
+    assert src.dim() == 2 and src.dtype == torch.bfloat16 and src.stride(1) == 1 and 1 <= len(dsts) <= 7
+    rows, cols = src.shape
+    ld = src.stride(0)
+    for d in dsts:
+        assert d.dtype == torch.bfloat16 and d.shape == src.shape and d.stride() == src.stride() and d.device == src.device
+    if rows == 0 or cols == 0:
+        return True
+    if cols % 8 or ld % 8 or src.data_ptr() % 16 or any(d.data_ptr() % 16 for d in dsts):
+        return False
+    dev = _lib.require_cuda(src, *dsts)
+    ptrs = (ctypes.c_void_p * len(dsts))(*[d.data_ptr() for d in dsts])
+    _call("quest_b200_copy_block_to_peers_cuda", dev, _lib.ptr(src), ptrs, len(dsts), rows, cols, ld, _lib.stream_of(src))
+    return True
 
 
 class layer_launches:

@@ -32,6 +32,7 @@ SIGNATURES = {
     "silu_mul_hadamard_quantize_int4_cuda_bf16": [_P, _P, _P, _P, _P, _I, _I, _I, _P],
     "fused_matmul_dequantize_a8_int4t_bf16_cuda": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     "quest_b200_prefers_a8": [_I, _I, _I],
+    "quest_b200_copy_block_to_peers_cuda": [_P, ctypes.POINTER(ctypes.c_void_p), _I, _I, _I, _LL, _P],
     "quest_b200_begin_layer": [],
     "quest_b200_end_layer": [],
     "hadamard_transform_cuda_bf16": [_P, _P, _I, _I, _I, _I, _P],

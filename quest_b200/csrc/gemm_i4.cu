@@ -27,6 +27,7 @@
 // Replaces gemm-quest/quest/matmul_kernel.cu:8-63 and gemm-quest/quest/fused_matmul_dequantize_kernel.cu
 // with gemm-quest/include/symmetric/** (CUTLASS 2.x Sm80 mma.sync kernels).
 #include <string.h>
+#include <type_traits>
 
 #include "tcgen05.cuh"
 
@@ -783,7 +784,7 @@ __device__ __forceinline__ void wide_convert_columns(const EpilogueParams& ep, c
 // A8 (single GPU only): the A operand arrives already as int8 in operand order (see hadamard_quant_tc_kernel<HB, true>):
 // one more warp copies its tiles with TMA (128-byte swizzle) straight into the int8 ring, the unpack warps handle
 // only B, and the main loop is bound by the MMAs instead of the unpack.
-template <bool FUSED, bool PUSH, bool A8 = false>
+template <bool FUSED, bool PUSH, bool A8 = false, bool CLIP = A8>
 __global__ void __launch_bounds__(PUSH ? wide::kThreads : (A8 ? wide::kThreads - 32 : wide::kThreads - 32 * wide::kPushWarps), 1)
 gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_d, const __grid_constant__ CUtensorMap tmap_d16,
@@ -1068,6 +1069,15 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         uint32_t it = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            // CLIP (a launch with tile columns narrower than 256): B rows beyond the tile's width (a multiple of 16, so the
+            // test is warp-uniform) are not unpacked.  A template parameter, not a run-time test: inside the plain loop the
+            // tests cost the packed variant 2-7 %.
+            int b_end = TM + TN;
+            if (CLIP) {
+                int n0, bn;
+                column_range(ep, tile / tiles_m, n0, bn);
+                b_end = TM + bn;
+            }
             for (int kb = 0; kb < num_kb; ++kb, ++it) {
                 const uint32_t ps = it % P_STAGES, pph = (it / P_STAGES) & 1u;
                 const uint32_t us = it % U_STAGES, uph = (it / U_STAGES) & 1u;
@@ -1083,12 +1093,13 @@ gemm_i4_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll
                     for (int i = 0; i < ITEMS / 2; ++i) {
                         const int item = t + (h * (ITEMS / 2) + i) * kUnpackWarps * 32;
-                        pk[i] = lds128(src + (item >> 2) * PK_ROW + (item & 3) * 16);
+                        if (!CLIP || (item >> 2) < b_end) pk[i] = lds128(src + (item >> 2) * PK_ROW + (item & 3) * 16);
                     }
 #pragma unroll
                     for (int i = 0; i < ITEMS / 2; ++i) {
                         const int item = t + (h * (ITEMS / 2) + i) * kUnpackWarps * 32;
                         const int r = item >> 2, c = item & 3;
+                        if (CLIP && r >= b_end) continue;
                         uint4 lo, hi;
                         unpack_x16(pk[i], lo, hi);
                         const uint32_t rowaddr = dst + r * U8_ROW;
@@ -1342,7 +1353,7 @@ static int make_a8_map(CUtensorMap* map, const void* base, int rows, int K) {
 // Tile columns of the 256-row kernel.  All 256 wide by default.  With `balance`, where more, narrower columns fill the
 // same number of waves over the SMs (M = 2048, N = 4096 on 148 SMs: 8 x 16 = 128 tiles leave 20 SMs idle; 8 x 18 tiles
 // of 224 or 240 columns use 144 and every CTA finishes 1/16 earlier), N is cut into that many columns instead.
-static void wide_columns(EpilogueParams* ep, int M, int N, int sms, bool balance) {
+static void wide_columns(EpilogueParams* ep, int M, int N, int sms, bool balance, int min_units = 12, int max_units = 15) {
     const int tiles_m = (M + wide::TM - 1) / wide::TM;
     ep->col_count = (N + wide::TN - 1) / wide::TN;
     ep->col_units = wide::TN / 16;
@@ -1355,7 +1366,7 @@ static void wide_columns(EpilogueParams* ep, int M, int N, int sms, bool balance
     const int most = (int)(waves * sms / tiles_m);  // the most columns that still fit these waves
     if (most <= ep->col_count) return;
     const int widest = (units + most - 1) / most;
-    if (widest >= wide::TN / 16 || widest < 12) return;  // nothing gained / tiles too narrow for this kernel
+    if (widest > max_units || widest < min_units) return;  // nothing gained / tiles too narrow for this variant
     ep->col_count = most;
     ep->col_units = units / most;
     ep->col_rem = units % most;
@@ -1399,19 +1410,24 @@ template <bool FUSED, bool PUSH>
 static int launch_gemm_wide_impl(const EpilogueParams& ep_in, const void* a, const void* b, int M, int K, int N, int sms,
                                  int dev, cudaStream_t stream) {
     EpilogueParams ep = ep_in;
-    static bool attr_set[64] = {false};
-    auto kernel = gemm_i4_wide_kernel<FUSED, PUSH>;
-    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+    // The unpack of both operands bounds this variant (about 3 cycles per operand row and K stage): a narrower tile saves
+    // its share of the B rows only, so widths of 224 and 240 gain nothing (measured: +1 %), but A comes packed (half the
+    // bytes of the int8 operand), so tiles of 128 ... 208 columns pay where they fill idle SMs or save a wave (K = 8192,
+    // M = 2048: N = 2560 -15 %, N = 5120 -17 %, N = 14336 -12 %).  The fused variants only.
+    wide_columns(&ep, M, N, sms, FUSED, 8, 13);
+    const bool clip = ep.col_units < wide::TN / 16;
+    static bool attr_set[2][64] = {{false}};
+    auto kernel = clip ? gemm_i4_wide_kernel<FUSED, PUSH, false, FUSED> : gemm_i4_wide_kernel<FUSED, PUSH, false, false>;
+    if (dev < 0 || dev >= 64 || !attr_set[clip][dev]) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, wide::SMEM_BYTES) != cudaSuccess)
             return QB200_ERR_CUDA;
-        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+        if (dev >= 0 && dev < 64) attr_set[clip][dev] = true;
     }
     CUtensorMap ma, mb;
     int st = make_packed_map(&ma, a, M, K, wide::TM);
     if (st != QB200_OK) return st;
     st = make_packed_map(&mb, b, N, K, wide::TN);
     if (st != QB200_OK) return st;
-    wide_columns(&ep, M, N, sms, false);  // the unpack of both operands bounds this variant: narrower tiles gain nothing
     const int tiles = ((M + wide::TM - 1) / wide::TM) * ep.col_count;
     const int grid = tiles < sms ? tiles : sms;
     const int threads = PUSH ? wide::kThreads : wide::kThreads - 32 * wide::kPushWarps;
@@ -1466,10 +1482,15 @@ static int pick_tile(int M, int N, int K, int sms, long long* est_cycles) {
         if (best_t < 0 || t < best_t) { best_t = t; best = bn; }
     }
     {
-        const long long tiles = (long long)((M + wide::TM - 1) / wide::TM) * ((N + wide::TN - 1) / wide::TN);
+        EpilogueParams cols{};
+        wide_columns(&cols, M, N, sms, true, 8, 13);  // the tile columns the 256-row kernel would use
+        const long long width = 16ll * (cols.col_units + (cols.col_rem > 0 ? 1 : 0));
+        const long long tiles = (long long)((M + wide::TM - 1) / wide::TM) * cols.col_count;
         const long long waves = (tiles + sms - 1) / sms;
-        const long long t = waves * (kb * 1536 + 7000);
-        if (t < best_t) { best_t = t; best = kWideTile; }
+        const long long t = waves * (kb * 3 * (wide::TM + width) + 7000 * width / wide::TN);
+        // narrow balanced tiles must beat the 128-row kernel clearly: at an estimated tie they measured 5 % slower
+        const bool clear = width == wide::TN || t * 21 < best_t * 20;
+        if (t < best_t && clear) { best_t = t; best = kWideTile; }
     }
     *est_cycles = best_t;
     return best;

@@ -929,6 +929,24 @@ __global__ void __launch_bounds__(256) add_mul_vv_scalar_kernel(__nv_bfloat16* _
     }
 }
 
+// One block of bf16 [rows, cols] (row stride ld_bytes in every buffer) copied from src to n_dst destinations with one
+// launch: the small-M exchange of the column-sharded layer (the block a rank has computed goes into every peer's
+// output, which is mapped into this address space: plain 16-byte peer stores).
+struct CopyDsts {
+    void* p[7];
+};
+
+__global__ void copy_block_kernel(const uint8_t* __restrict__ src, const CopyDsts dsts, const int n_dst, const int rows,
+                                  const int chunks, const long long ld_bytes) {
+    const int total = rows * chunks;
+    for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+        const int r = idx / chunks, c = idx - r * chunks;
+        const long long off = (long long)r * ld_bytes + (long long)c * 16;
+        const uint4 v = *reinterpret_cast<const uint4*>(src + off);
+        for (int d = 0; d < n_dst; ++d) *reinterpret_cast<uint4*>(static_cast<uint8_t*>(dsts.p[d]) + off) = v;
+    }
+}
+
 }  // namespace qb
 
 // -------------------------------------------------------------------------------------------------
@@ -1154,5 +1172,26 @@ extern "C" int add_mul_vv_cuda_bf16(void* mat_d, const void* vec_a_add, const vo
         add_mul_vv_vec8_kernel<<<(unsigned)blocks, 256, 0, stream>>>(d, aa, am, ba, bm, c, size_a, size_b);
     else
         add_mul_vv_scalar_kernel<<<(unsigned)blocks, 256, 0, stream>>>(d, aa, am, ba, bm, c, size_a, size_b);
+    return launch_status();
+}
+
+extern "C" int quest_b200_copy_block_to_peers_cuda(const void* src, void* const* dsts, int n_dst, int rows, int cols,
+                                                   long long ld, cudaStream_t stream) {
+    if (rows < 0 || cols < 0 || n_dst < 0 || n_dst > 7 || ld < cols) return QB200_ERR_INVALID_ARGUMENT;
+    if (rows == 0 || cols == 0 || n_dst == 0) return QB200_OK;
+    if (!src || !dsts) return QB200_ERR_INVALID_ARGUMENT;
+    if (cols % 8 != 0 || ld % 8 != 0 || !aligned16(src)) return QB200_ERR_UNSUPPORTED;  // whole 16-byte pieces only
+    CopyDsts d{};
+    for (int i = 0; i < n_dst; ++i) {
+        if (!dsts[i]) return QB200_ERR_INVALID_ARGUMENT;
+        if (!aligned16(dsts[i])) return QB200_ERR_UNSUPPORTED;
+        d.p[i] = dsts[i];
+    }
+    const int chunks = cols / 8;
+    const long long total = (long long)rows * chunks;
+    if (total > (1ll << 30)) return QB200_ERR_UNSUPPORTED;
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    copy_block_kernel<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const uint8_t*>(src), d, n_dst, rows, chunks, ld * 2);
     return launch_status();
 }

@@ -155,8 +155,10 @@ class ShardedLinear4bit:
                 self._stage = stage
                 self.compute_shard(x, mine, ws)
                 self._stage = None
-                for i in range(1, self.world):
-                    views[(self.rank + i) % self.world][:, self.n0:self.n1].copy_(mine)
+                theirs = [views[(self.rank + i) % self.world][:, self.n0:self.n1] for i in range(1, self.world)]
+                if not quest.copy_block_to_peers(mine, theirs):  # one launch for all peers where the block is 16-byte tiled
+                    for dst in theirs:
+                        dst.copy_(mine)
             else:
                 off = self.n0 * t.element_size()
                 order = [self.rank] + [(self.rank + i) % self.world for i in range(1, self.world)]

@@ -479,3 +479,25 @@ def test_one_call_layer_on_the_int8_operand_route(m, k, n):
         assert outs[0].equal(ya) and outs[2].equal(ya) and outs[1].equal(yb[3]) and outs[3].equal(yb[3])
         assert a8.equal(yb[0]) and sc.equal(yb[1]) and rs.equal(yb[2])
     assert quest.device_status() == 0
+
+
+# ------------------------------------------------------------------ few-row exchange of the sharded layer ---
+@pytest.mark.parametrize("rows,cols,n_dst", [(16, 3584, 7), (1, 1280, 3), (5, 1024, 1), (16, 8, 2)])
+def test_copy_block_to_peers_writes_exactly_the_block(rows, cols, n_dst):
+    """One launch copies a column block into the same place of up to seven other buffers (here all on this GPU; in the
+    sharded layer they are the peers' outputs) and touches nothing around it; views that are not 16-byte tiled are refused
+    without a copy."""
+    n_total, n0 = cols * 3 + 64, cols + 32
+    g = torch.Generator(device=DEV).manual_seed(rows + cols)
+    bufs = [torch.randn(rows, n_total, device=DEV, generator=g).to(torch.bfloat16) for _ in range(n_dst + 1)]
+    before = [b.clone() for b in bufs]
+    src = bufs[0][:, n0:n0 + cols]
+    assert quest.copy_block_to_peers(src, [b[:, n0:n0 + cols] for b in bufs[1:]])
+    torch.cuda.synchronize()
+    assert bufs[0].equal(before[0])
+    for b, old in zip(bufs[1:], before[1:]):
+        assert b[:, n0:n0 + cols].equal(before[0][:, n0:n0 + cols])
+        assert b[:, :n0].equal(old[:, :n0]) and b[:, n0 + cols:].equal(old[:, n0 + cols:])
+    odd = [b[:, 3:3 + cols] for b in bufs]  # starts 6 bytes into a row: not 16-byte aligned
+    assert not quest.copy_block_to_peers(odd[0], odd[1:])
+    assert quest.device_status() == 0

@@ -1353,7 +1353,8 @@ static int make_a8_map(CUtensorMap* map, const void* base, int rows, int K) {
 // Tile columns of the 256-row kernel.  All 256 wide by default.  With `balance`, where more, narrower columns fill the
 // same number of waves over the SMs (M = 2048, N = 4096 on 148 SMs: 8 x 16 = 128 tiles leave 20 SMs idle; 8 x 18 tiles
 // of 224 or 240 columns use 144 and every CTA finishes 1/16 earlier), N is cut into that many columns instead.
-static void wide_columns(EpilogueParams* ep, int M, int N, int sms, bool balance, int min_units = 12, int max_units = 15) {
+static void wide_columns(EpilogueParams* ep, int M, int N, int sms, bool balance, int min_units = 12, int max_units = 15,
+                         int align_units = 1) {
     const int tiles_m = (M + wide::TM - 1) / wide::TM;
     ep->col_count = (N + wide::TN - 1) / wide::TN;
     ep->col_units = wide::TN / 16;
@@ -1365,7 +1366,17 @@ static void wide_columns(EpilogueParams* ep, int M, int N, int sms, bool balance
     const long long waves = ((long long)tiles_m * ep->col_count + sms - 1) / sms;
     const int most = (int)(waves * sms / tiles_m);  // the most columns that still fit these waves
     if (most <= ep->col_count) return;
-    const int widest = (units + most - 1) / most;
+    int widest = (units + most - 1) / most;
+    if (align_units > 1) {
+        // Every column equally wide, a multiple of align_units * 16 (64 columns = 128 bytes of bf16): what the multi-GPU
+        // variant needs, whose 64-column bulk stores to the peers should cover whole 128-byte lines and no column twice.
+        widest = (widest + align_units - 1) / align_units * align_units;
+        if (widest > max_units || widest < min_units) return;
+        ep->col_count = (units + widest - 1) / widest;
+        ep->col_units = widest;
+        ep->col_rem = 0;
+        return;
+    }
     if (widest > max_units || widest < min_units) return;  // nothing gained / tiles too narrow for this variant
     ep->col_count = most;
     ep->col_units = units / most;
@@ -1413,8 +1424,11 @@ static int launch_gemm_wide_impl(const EpilogueParams& ep_in, const void* a, con
     // The unpack of both operands bounds this variant (about 3 cycles per operand row and K stage): a narrower tile saves
     // its share of the B rows only, so widths of 224 and 240 gain nothing (measured: +1 %), but A comes packed (half the
     // bytes of the int8 operand), so tiles of 128 ... 208 columns pay where they fill idle SMs or save a wave (K = 8192,
-    // M = 2048: N = 2560 -15 %, N = 5120 -17 %, N = 14336 -12 %).  The fused variants only.
-    wide_columns(&ep, M, N, sms, FUSED, 8, 13);
+    // M = 2048: N = 2560 -15 %, N = 5120 -17 %, N = 14336 -12 %).  The fused variants only.  With peers the widths are
+    // multiples of 64 columns: with 144-column tiles the last, overlapping 64-column piece sent 48 columns a second time
+    // and no piece covered whole 128-byte lines, and the exchange of a 4-GPU step grew from 51 to 91 us.  With a single
+    // peer the narrower tiles won all the same (2 GPUs, M = 2048, K = 8192, N = 14336 per rank: step 262 -> 242 us).
+    wide_columns(&ep, M, N, sms, FUSED, 8, 13, PUSH && ep.n_peer > 1 ? 4 : 1);
     const bool clip = ep.col_units < wide::TN / 16;
     static bool attr_set[2][64] = {{false}};
     auto kernel = clip ? gemm_i4_wide_kernel<FUSED, PUSH, false, FUSED> : gemm_i4_wide_kernel<FUSED, PUSH, false, false>;

@@ -862,6 +862,18 @@ def run_c4(args):
                    "f1_us": t_f1 * 1e6, "f1_gbs": (2.5 * m * k + 6.0 * m) / t_f1 / 1e9,
                    "gemm_plus_f1_us": (t_gemm + t_f1) * 1e6,
                    "aggregate_tops_gemm_plus_f1": 2.0 * m * n_total * k / (t_gemm + t_f1) / 1e12}
+            if world == 1:
+                # the whole layer as linear_forward runs it on one GPU: the route the library prefers for the shape (int8
+                # operand with balanced tile columns where the 256-row kernel applies), one call, dependent launches
+                a8 = quest.prefers_a8(m, k, n_local)
+                codes = torch.empty(m, k if a8 else k // 2, dtype=torch.uint8, device=dev)
+                ws_kw = {"_a_int8": codes} if a8 else {"_a_int_packed": codes}
+                t_layer = timed(lambda: quest.linear_forward(x, wp, ws, wa, out=local, _a_scale=sc, _a_int_row_sum=rs,
+                                                             use_hadamard=True, block=args.block, **ws_kw))
+                row["layer_us"] = t_layer * 1e6
+                row["layer_route"] = "int8 operand" if a8 else "packed int4"
+                row["aggregate_tops_layer"] = 2.0 * m * n_total * k / t_layer / 1e12
+                del codes
             if world > 1:
                 delivered = {}
                 for exch in ("push", "nccl"):

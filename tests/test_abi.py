@@ -57,6 +57,19 @@ def test_argument_validation_without_gpu():
     assert lib.matmul_int4_int4t_int32_cuda(p, p + 1, p, 4, 128, 4, None) == 1    # misaligned operand
     assert lib.quantize_int4_cuda_bf16(p, p, None, p, None, 7, 1, 0, None) == 1   # packed output needs even K
     assert lib.add_mul_vv_cuda_bf16(None, None, None, None, None, None, 0, 8, None) == 0
+    # the one-call layer and the block copy validate before they launch, too
+    assert lib.w4a4_linear_hadamard_bf16_cuda(p, p, p, p, p, p, p, None, 4, 128, 4, 128, None) == 1     # row sums required
+    assert lib.w4a4_linear_hadamard_a8_bf16_cuda(p, p, p, p, p, p, p, None, 4, 128, 4, 128, None) == 1
+    dsts = (ctypes.c_void_p * 2)(p + 256, p + 512)
+    assert lib.quest_b200_copy_block_to_peers_cuda(p, dsts, 2, 0, 64, 64, None) == 0                      # nothing to copy
+    assert lib.quest_b200_copy_block_to_peers_cuda(p, dsts, 8, 4, 64, 64, None) == 1                      # at most 7 destinations
+    assert lib.quest_b200_copy_block_to_peers_cuda(p, dsts, 2, 4, 64, 32, None) == 1                      # ld < cols
+    assert lib.quest_b200_copy_block_to_peers_cuda(p, dsts, 2, 4, 60, 64, None) == 2                      # not whole 16-byte pieces
+    odd = (ctypes.c_void_p * 2)(p + 256, p + 514)
+    assert lib.quest_b200_copy_block_to_peers_cuda(p, odd, 2, 4, 64, 64, None) == 2                       # misaligned destination
+    # layer mode is host-thread state: begin / end always succeed and leave the ordinary entry points usable
+    assert lib.quest_b200_begin_layer() == 0 and lib.quest_b200_end_layer() == 0
+    assert lib.matmul_int4_int4t_int32_cuda(None, None, None, 0, 128, 4, None) == 0
 
 
 def test_no_cpu_fallback():
